@@ -1,0 +1,126 @@
+/*
+ * kvq_b200 -- C ABI of the static per-channel INT8 KV-cache kernels for NVIDIA B200 (sm_100a).
+ *
+ * Drop-in boundary for the native module of ischencheng/int8-kvcache: each entry point below replaces one
+ * function of the reference's pybind module (kvq/cuda/int8_kv.cu:674-679). The reference passes torch
+ * tensors; here every tensor is a raw device pointer plus its sizes and element strides, and the CUDA
+ * stream is explicit. Nothing in this library allocates device memory, synchronizes the device or
+ * depends on PyTorch; all entry points only enqueue work on `stream` and can be captured in a CUDA graph.
+ *
+ * Conventions
+ *   - bf16 tensors are `const void*` to 2-byte bfloat16 elements, int8 caches are `void*` to 1-byte elements.
+ *   - Strides are in ELEMENTS of the tensor they describe. The innermost (head_dim) stride is always 1.
+ *   - Caches are views [num_blocks, block_size, num_kv_heads, head_dim] with arbitrary block/slot/head
+ *     strides (the vLLM layout interleaves K and V; separate contiguous caches work too).
+ *   - Scales are fp32, contiguous: [num_kv_heads, head_dim] ("per channel") or [num_kv_heads] ("per head"),
+ *     selected by the k_per_channel / v_per_channel flags. k_mu is always [num_kv_heads, head_dim].
+ *   - head_dim is 64 or 128. Rows of bf16 tensors and cache rows must be 16-byte aligned.
+ *   - Return value: KVQ_OK, or an error code with a message available from kvq_last_error() on the
+ *     calling thread. Empty batches return KVQ_OK without launching anything.
+ */
+#ifndef KVQ_B200_H_
+#define KVQ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define KVQ_OK 0
+#define KVQ_ERR_INVALID_ARGUMENT 1 /* shape / layout violation (the reference raises TORCH_CHECK -> RuntimeError) */
+#define KVQ_ERR_CUDA 2             /* a CUDA runtime or driver call failed */
+#define KVQ_ERR_WORKSPACE 3        /* workspace missing or too small */
+
+/* cudaStream_t without pulling in the CUDA headers. */
+typedef struct CUstream_st* kvq_stream_t;
+
+/* Library version (major * 10000 + minor * 100 + patch). */
+int kvq_version(void);
+
+/* Message of the last error returned on this thread ("" if none). The pointer stays valid until the next
+ * failing call on the same thread. */
+const char* kvq_last_error(void);
+
+/*
+ * Fused static quantize + paged cache write.
+ * Replaces quant_cache(key, value, kc, vc, slots, ks, vs, kmu), kvq/cuda/int8_kv.cu:554-575 (kernel :55-84).
+ *   k_i8 = clamp(rne((f32(key) - k_mu) / k_scale), +-127), v_i8 = clamp(rne(f32(value) / v_scale), +-127),
+ *   written to cache[slot / block_size][slot % block_size][head][:]. Rows with slot < 0 are skipped; rows of
+ *   key/value beyond num_tokens are ignored. Bit-exact with the reference's torch quantizer.
+ * key/value: bf16 [>= num_tokens, num_kv_heads, head_dim] with token/head strides; slots: int64 [num_tokens].
+ */
+int kvq_quant_cache(const void* key, const void* value, void* k_cache, void* v_cache, const int64_t* slots,
+                    const float* k_scale, const float* v_scale, const float* k_mu, int64_t num_tokens,
+                    int num_kv_heads, int head_dim, int block_size, int64_t key_stride_t, int64_t key_stride_h,
+                    int64_t value_stride_t, int64_t value_stride_h, int64_t kc_stride_b, int64_t kc_stride_n,
+                    int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h,
+                    int k_per_channel, int v_per_channel, kvq_stream_t stream);
+
+/*
+ * Standalone q quantization: fold the per-channel K scale into q, one dynamic scale per `group` channels.
+ * Replaces quant_q(q, ks, group), kvq/cuda/int8_kv.cu:577-598 (kernel :89-111). Unlike the reference this
+ * entry point does not allocate: the caller passes q_i8 [T, Hq, head_dim] (contiguous int8) and
+ * q_scale [T, Hq, head_dim / group] (contiguous fp32). head_dim must be 128 and group 128 or 32, as in the
+ * reference. k_scale is [Hkv, 128] when k_per_channel, otherwise it is not read.
+ */
+int kvq_quant_q(const void* q, const float* k_scale, void* q_i8, float* q_scale, int64_t num_tokens,
+                int num_q_heads, int num_kv_heads, int head_dim, int group, int64_t q_stride_t, int64_t q_stride_h,
+                int k_per_channel, kvq_stream_t stream);
+
+/*
+ * Bytes of scratch kvq_int8_decode_attention needs on the current device for a batch of `num_seqs` requests
+ * (split-KV partial results, the work plan, a status word). The size does not depend on context lengths.
+ * Has no counterpart in the reference, which borrows vLLM's Triton split-KV buffers
+ * (kvq/vllm_int8/backend.py:175-177).
+ */
+size_t kvq_decode_workspace_size(int num_seqs, int head_dim);
+
+/*
+ * INT8 paged attention for requests with 1 <= q_len <= qmax query tokens (decode, speculative-decoding
+ * verification), causal inside the query. Requests with q_len == 0 or q_len > qmax are skipped and their
+ * output rows are left untouched.
+ * Replaces int8_decode_attention(...), kvq/cuda/int8_kv.cu:600-648 (kernels :168-463 and :472-503).
+ *   q, out: bf16 [T, Hq, head_dim]; cu_q: int32 [num_seqs + 1]; seq_lens: int32 [>= num_seqs];
+ *   block_table: int32 [>= num_seqs, bt_stride]; block_size: power of two >= 16; qmax <= 8.
+ * Numerics ("implementation B"): q' = q * k_scale (per channel), quantized per (token, head); scores from
+ * int8 x int8 -> int32 tensor-core products; fp32 online softmax; P quantized to int8 per (row, 32-key tile
+ * at absolute positions); P.V in int8 -> int32; denominator from the quantized P; output * v_scale -> bf16.
+ * Split-KV is chosen internally (work is divided evenly over the SMs) and merged by a second kernel; both
+ * use `workspace` (>= kvq_decode_workspace_size bytes, 256-byte aligned). Calls that share a workspace must
+ * not overlap on the GPU.
+ */
+int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
+                              const int32_t* cu_q, const int32_t* seq_lens, const int32_t* block_table,
+                              const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+                              int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+                              int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t, int64_t o_stride_h,
+                              int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h, int64_t vc_stride_b,
+                              int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride, int k_per_channel,
+                              int v_per_channel, int max_query_len, int qmax, void* workspace,
+                              size_t workspace_bytes, kvq_stream_t stream);
+
+/*
+ * Debug helper: copy the status word the attention kernels keep in `workspace` to the host (synchronizes
+ * `stream`). 0 = clean; non-zero = a bounded wait inside a kernel expired. No reference counterpart.
+ */
+int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream);
+
+/*
+ * Dequantize pages of the INT8 cache into a temporary bf16 paged cache for the long-query (prefill) path.
+ * Replaces dequant_pages(kc, vc, ko, vo, block_table, src_req, src_j, ks, vs), kvq/cuda/int8_kv.cu:650-672
+ * (kernel :511-542). Output page p = bf16(rne(int8 page block_table[src_req[p]][src_j[p]] * scale)), laid out
+ * contiguously as [num_pages, block_size, num_kv_heads, head_dim]; K stays (k - k_mu).
+ */
+int kvq_dequant_pages(const void* k_cache, const void* v_cache, void* k_out, void* v_out,
+                      const int32_t* block_table, const int32_t* src_req, const int32_t* src_j,
+                      const float* k_scale, const float* v_scale, int64_t num_pages, int num_kv_heads, int head_dim,
+                      int block_size, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
+                      int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+                      int k_per_channel, int v_per_channel, kvq_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KVQ_B200_H_ */

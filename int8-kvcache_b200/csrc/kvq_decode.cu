@@ -1,0 +1,827 @@
+// INT8 paged attention for short queries (decode and speculative-decoding verification) on sm_100a.
+//
+// Three launches per call, all on the caller's stream, no host synchronization:
+//   plan_kernel     one block: per-request work in 32-key units, exclusive prefix sum, units per CTA
+//   decode_kernel   one CTA per slice of the global unit range (the range is cut evenly over
+//                   #SMs x resident CTAs, so every CTA streams the same number of KV bytes whatever the
+//                   mix of context lengths); a slice covers whole (request, kv head, m tile) items and at
+//                   most two partial ones, whose (acc, max, sum) go to the workspace
+//   merge_kernel    items that were cut across CTAs: combine their partials into the output
+//
+// Inside decode_kernel each warp owns a ring of NSTAGE stages fed by TMA (cp.async.bulk.tensor, 128-byte
+// swizzle, one 16-key x head_dim box per page half, completion on an mbarrier) and works on its own
+// 32-key chunks: S = Q.K^T with mma.sync m16n8k32 s8 (K fragments by ldmatrix), fp32 online softmax in the
+// exp2 domain, P quantized to int8 per (row, chunk), O += P.V with the same mma (V fragments by the 8-bit
+// transposing ldmatrix of sm_100), then the warps of the CTA are combined through shared memory.
+//
+// Numerics follow "implementation B" of the reference (kvq/int8_ref.py:108-143, kernel restatement
+// kvq/cuda/int8_kv.cu:11-15): see include/kvq_b200.h.
+#include <cuda.h>
+
+#include <mutex>
+#include <vector>
+
+#include "kvq_common.cuh"
+
+namespace kvq {
+namespace {
+
+constexpr int CHUNK = 32;      // keys per pipeline stage and per P-quantization tile
+constexpr int NWARPS = 4;
+constexpr int NTHREADS = NWARPS * 32;
+constexpr int NSTAGE = 3;      // TMA ring depth per warp
+constexpr int MIN_UNITS = 4;   // never give a CTA less than one chunk per warp
+constexpr int MAX_CTAS_PER_SM = 4;
+constexpr int HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total units, [2] units per CTA
+constexpr int PART_ROWS = 16;
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;
+  __nv_bfloat16* out;
+  const int32_t *cu_q, *seq_lens, *block_table;
+  const float *ks, *vs;
+  int32_t* hdr;
+  const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units
+  float* part_acc;         // [grid * 2][16][D]  numerator * v_scale of a cut item
+  float* part_ml;          // [grid * 2][16][2]  running max of the scores, denominator
+  double sm_scale;       // softmax scale, natural-log domain
+  int num_seqs, Hq, Hkv, G, lbs, bs_mask, qmax;
+  int64_t q_st, q_sh, o_st, o_sh, bt_stride;
+  int pc_k, pc_v;
+  int kpos[3], vpos[3];    // tensor-map coordinate slot (1..3) of the (slot-in-block, head, block) dims
+};
+
+// ------------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2^31 clock cycles (about a second) and reports failure instead of hanging.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > (1ll << 31)) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// Two 16x16 byte matrices, transposed: with lane l pointing at row l of a [32 keys][16 channels] block, lane
+// (g = l / 4, t = l % 4) receives r0 = rows 4t..4t+3 of column g, r1 = same rows of column g + 8, and r2, r3
+// the same for rows 16 + 4t.. : the B fragments (k = keys, n = channels) of two m16n8k32 tiles.
+__device__ __forceinline__ void ldsm_t8_x2(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m16n16.x2.trans.shared.b8 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+constexpr float LOG2E = 1.4426950408889634f;
+
+// fp32(dot * c) for c = hi + lo: the product is formed to ~48 bits and rounded once, like the reference's
+// float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100 that moves
+// P = exp(score - max) by 1e-5 and flips its int8 quantization far more often than the reference's own noise.
+__device__ __forceinline__ float score(int dot, float hi, float lo) {
+  const float d = static_cast<float>(dot);  // |dot| < 2^24: exact
+  const float p = d * hi;
+  return p + fmaf(d, lo, fmaf(d, hi, -p));
+}
+
+// Byte offset of (key row tau, 16-byte column c16) inside a TMA-written tile of D-byte rows. The tile base
+// is 1024-byte aligned; TMA's 128B swizzle XORs address bits [4:6] with bits [7:9] (64B: bits [4:5] with [7:8]).
+template <int D>
+__device__ __forceinline__ uint32_t tile_off(int tau, int c16) {
+  const uint32_t off = tau * D + c16 * 16;
+  return off ^ (((off >> 7) & (D == 128 ? 7u : 3u)) << 4);
+}
+
+__device__ __forceinline__ int units_of(int qlen, int L, int G, int Hkv, int qmax, int& nchunks, int& mtiles) {
+  nchunks = max(1, (L + CHUNK - 1) / CHUNK);
+  mtiles = (qlen * G + 15) / 16;
+  return (qlen < 1 || qlen > qmax) ? 0 : nchunks * Hkv * mtiles;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// plan: units per request, exclusive prefix sum, units per CTA
+// ------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_lens,
+                                                   int num_seqs, int G, int Hkv, int qmax, int nctas,
+                                                   int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
+  __shared__ int s_warp[8];
+  __shared__ int s_carry;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_carry = 0, hdr[0] = 0;
+  __syncthreads();
+  for (int base = 0; base < num_seqs; base += 256) {
+    const int r = base + tid;
+    int u = 0;
+    if (r < num_seqs) {
+      int nc, mt;
+      u = units_of(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, nc, mt);
+    }
+    int x = u;  // inclusive scan inside the warp
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_warp[warp] = x;
+    __syncthreads();
+    int woff = 0;
+    for (int w = 0; w < warp; ++w) woff += s_warp[w];
+    const int carry = s_carry;
+    if (r < num_seqs) prefix[r] = carry + woff + x - u;
+    __syncthreads();
+    if (tid == 255) s_carry = carry + woff + x;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    const int total = s_carry;
+    prefix[num_seqs] = total;
+    hdr[1] = total;
+    hdr[2] = max((total + nctas - 1) / nctas, MIN_UNITS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// main kernel
+// ------------------------------------------------------------------------------------------------------
+template <int D>
+struct Geom {
+  static constexpr int TILE = CHUNK * D;          // one K or V chunk
+  static constexpr int STAGE = 2 * TILE;          // K chunk + V chunk
+  static constexpr int RING = NWARPS * NSTAGE * STAGE;
+  static constexpr int QROW = D + 16;             // s_q row stride: conflict-free A-fragment loads
+  static constexpr int ACC_RS = D + 8;            // combine buffer row stride in floats
+  static constexpr int SMALL = 16 * QROW + (32 + 2 * NWARPS * 16 + 32) * 4;
+  static constexpr int SMEM = 1024 + RING + SMALL;  // 1024: manual alignment of the ring
+  static_assert(NWARPS * 16 * ACC_RS * 4 <= RING, "combine buffer aliases the ring");
+};
+
+template <int D, bool ROWS16>
+__global__ void __launch_bounds__(NTHREADS, 2)
+    decode_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+  using Gm = Geom<D>;
+  constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS;
+  constexpr int NROWS = ROWS16 ? 16 : 8;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[NWARPS * NSTAGE];
+  __shared__ int s_req;
+
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  int8_t* s_q = reinterpret_cast<int8_t*>(ring_ptr + Gm::RING);
+  float* s_chi = reinterpret_cast<float*>(ring_ptr + Gm::RING + 16 * QROW);  // [16] score scale, high part
+  float* s_clo = s_chi + 16;            // [16] score scale, low part
+  float* s_m = s_clo + 16;              // [NWARPS][16]
+  float* s_l = s_m + NWARPS * 16;       // [NWARPS][16]
+  float* s_M = s_l + NWARPS * 16;       // [16] combined max
+  float* s_inv = s_M + 16;              // [16] 1 / combined denominator (direct) or denominator (partial)
+  float* s_acc = reinterpret_cast<float*>(ring_ptr);  // [NWARPS][NROWS][ACC_RS], valid between chunk loops
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int total = a.hdr[1], W = a.hdr[2];
+  const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
+  if (ubeg >= uend) return;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int i = 0; i < NWARPS * NSTAGE; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fence_proxy_async();
+  __syncthreads();
+
+  const uint32_t wring = ring + warp * NSTAGE * Gm::STAGE;
+  const uint32_t wbar = smem_u32(&s_bar[warp * NSTAGE]);
+  uint32_t gbase = 0;  // chunks this warp has pushed through its ring so far (stage and phase bookkeeping)
+  bool ok = true;
+
+  // Lane-constant pieces of the ldmatrix addresses.
+  // K (non-transposed, 4 matrices of 8 keys x 16 channels): lane l addresses key (l & 7) of matrix l >> 3.
+  // V (transposed 16x16 bytes): lane l addresses key vrow(l), chosen so that a lane's four bytes are the keys
+  //   {2t, 2t+1, 8+2t, 9+2t} (+16 for the second matrix): the keys whose scores the same lane holds after QK.
+  const int krow = lane & 7, kmat = lane >> 3;
+  const int vrow = (lane & 1) + 8 * ((lane >> 1) & 1) + 2 * ((lane >> 2) & 3) + 16 * (lane >> 4);
+
+  int u = ubeg;
+  bool first_seg = true;
+  while (u < uend) {
+    // ---- find the request that owns unit u: prefix[r] <= u < prefix[r + 1] ----
+    for (int r = tid; r < a.num_seqs; r += NTHREADS)
+      if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
+    __syncthreads();
+    const int req = s_req;
+    const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
+    int nchunks, mtiles;
+    units_of(qlen, L, a.G, a.Hkv, a.qmax, nchunks, mtiles);
+    const int p0 = a.prefix[req], p1 = a.prefix[req + 1];
+    const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
+
+    // ---- items (kv head, m tile) of this request that intersect [u, uend) ----
+    while (u < uend && u < p1) {
+      const int item = (u - p0) / nchunks, c0 = (u - p0) - item * nchunks;
+      const int kvh = item / mtiles, mt = item - kvh * mtiles;
+      const int c1 = min(nchunks, c0 + (uend - u));
+      const bool whole = (c0 == 0 && c1 == nchunks);
+      const int nw = (c1 - c0 - warp + NWARPS - 1) / NWARPS;  // chunks of this warp: c0 + warp + NWARPS * i
+
+      // -- TMA producer (per warp): page ids 16 chunks at a time, one lane per 16-key half chunk --
+      int pg_cur = 0, pg_next = 0;
+      auto load_pages = [&](int batch) {
+        const int i = 16 * batch + (lane >> 1);
+        int pg = 0;
+        if (i < nw) {
+          const int c = c0 + warp + NWARPS * i;
+          const int n0 = c * CHUNK + (lane & 1) * 16;
+          pg = bt[(n0 < L ? n0 : c * CHUNK) >> a.lbs];
+        }
+        return pg;
+      };
+      auto issue = [&](int i) {
+        if ((i & 15) == 0) {
+          pg_cur = (i == 0) ? load_pages(0) : pg_next;
+          pg_next = load_pages((i >> 4) + 1);
+        }
+        const int pa = __shfl_sync(0xffffffffu, pg_cur, 2 * (i & 15));
+        const int pb = __shfl_sync(0xffffffffu, pg_cur, 2 * (i & 15) + 1);
+        if (lane == 0) {
+          const uint32_t gi = gbase + i, st = gi % NSTAGE;
+          const uint32_t bar = wbar + st * 8, dst = wring + st * Gm::STAGE;
+          const int c = c0 + warp + NWARPS * i;
+          mbar_expect_tx(bar, Gm::STAGE);
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            const int n0 = c * CHUNK + half * 16;
+            const int off = (n0 < L ? n0 : c * CHUNK) & a.bs_mask;
+            const int page = half ? pb : pa;
+            // coordinate slot s holds whichever of (offset in block, head, block) the tensor map put there
+            auto coord = [&](const int (&pos)[3], int s) { return pos[0] == s ? off : (pos[1] == s ? kvh : page); };
+            tma_load_4d(dst + half * 16 * D, &tm_k, 0, coord(a.kpos, 1), coord(a.kpos, 2), coord(a.kpos, 3), bar);
+            tma_load_4d(dst + Gm::TILE + half * 16 * D, &tm_v, 0, coord(a.vpos, 1), coord(a.vpos, 2),
+                        coord(a.vpos, 3), bar);
+          }
+        }
+      };
+      int issued = 0;
+      if (ok)
+        for (; issued < min(nw, NSTAGE - 1); ++issued) issue(issued);
+
+      // -- q prologue: fold s_k, quantize per row; 8 threads per row. Done in double like the reference's
+      //    implementation B (exact products, double scale and division); it runs once per item. --
+      {
+        constexpr int CPT = D / 8;
+        const int row = tid >> 3, part = tid & 7, d0 = part * CPT;
+        const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+        float x[CPT];   // fp32(q * s_k): what gets quantized
+        double amax = 0.0;
+#pragma unroll
+        for (int e = 0; e < CPT; ++e) x[e] = 0.f;
+        if (rt < qlen) {
+          const __nv_bfloat16* qp = a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0;
+#pragma unroll
+          for (int v8 = 0; v8 < CPT / 8; ++v8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(qp + 8 * v8);
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) x[8 * v8 + 2 * k] = bf16lo(w[k]), x[8 * v8 + 2 * k + 1] = bf16hi(w[k]);
+          }
+#pragma unroll
+          for (int e = 0; e < CPT; ++e) {
+            const double xd = a.pc_k ? static_cast<double>(x[e]) * static_cast<double>(__ldg(a.ks + kvh * D + d0 + e))
+                                     : static_cast<double>(x[e]);
+            amax = fmax(amax, fabs(xd));
+            x[e] = static_cast<float>(xd);
+          }
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) amax = fmax(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const double sq = fmax(amax / 127.0, 1e-8);
+        uint32_t w[CPT / 4];
+#pragma unroll
+        for (int k = 0; k < CPT / 4; ++k) {
+          int b[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            b[e] = max(-127, min(127, __double2int_rn(static_cast<double>(x[4 * k + e]) / sq)));
+          w[k] = pack4(b[0], b[1], b[2], b[3]);
+        }
+        if constexpr (CPT == 16)
+          *reinterpret_cast<uint4*>(&s_q[row * QROW + d0]) = make_uint4(w[0], w[1], w[2], w[3]);
+        else
+          *reinterpret_cast<uint2*>(&s_q[row * QROW + d0]) = make_uint2(w[0], w[1]);
+        if (part == 0) {
+          // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
+          const double c = sq * (a.pc_k ? 1.0 : static_cast<double>(__ldg(a.ks + kvh))) * a.sm_scale;
+          const float hi = static_cast<float>(c);
+          s_chi[row] = hi;
+          s_clo[row] = static_cast<float>(c - static_cast<double>(hi));
+        }
+      }
+      __syncthreads();
+      uint32_t qa[KSTEPS][4];
+#pragma unroll
+      for (int s = 0; s < KSTEPS; ++s) {
+        qa[s][0] = *reinterpret_cast<const uint32_t*>(&s_q[g * QROW + 32 * s + 4 * t]);
+        qa[s][2] = *reinterpret_cast<const uint32_t*>(&s_q[g * QROW + 32 * s + 16 + 4 * t]);
+        qa[s][1] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&s_q[(g + 8) * QROW + 32 * s + 4 * t]) : 0u;
+        qa[s][3] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&s_q[(g + 8) * QROW + 32 * s + 16 + 4 * t]) : 0u;
+      }
+      const float ch0 = s_chi[g], cl0 = s_clo[g], ch1 = s_chi[g + 8], cl1 = s_clo[g + 8];
+      // causal key limit per row: key n is visible iff n < L - qlen + 1 + (query token of the row)
+      auto row_lim = [&](int r) {
+        const int rt = (mt * 16 + r) / a.G;
+        return rt < qlen ? L - qlen + 1 + rt : L;
+      };
+      const int lim0 = row_lim(g), lim1 = row_lim(g + 8);
+      const int lim_all = L - qlen + 1;  // every row sees keys below this
+
+      float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
+      float acc[NT][ROWS16 ? 4 : 2];
+#pragma unroll
+      for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < (ROWS16 ? 4 : 2); ++e) acc[j][e] = 0.f;
+
+      // -- main loop over this warp's chunks --
+      for (int i = 0; i < nw && ok; ++i) {
+        if (issued < nw) issue(issued++);
+        const uint32_t gi = gbase + i, st = gi % NSTAGE;
+        ok = __all_sync(0xffffffffu, mbar_wait(wbar + st * 8, (gi / NSTAGE) & 1));
+        if (!ok) break;
+        const uint32_t sk = wring + st * Gm::STAGE, sv = sk + Gm::TILE;
+        const int n_base = (c0 + warp + NWARPS * i) * CHUNK;
+
+        // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
+        int sacc[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
+#pragma unroll
+          for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
+            uint32_t b[4];
+            ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat));
+            mma_s8(sacc[j], qa[2 * s2], b[0], b[1]);
+            mma_s8(sacc[j], qa[2 * s2 + 1], b[2], b[3]);
+          }
+        }
+        // accumulator (j, e) of lane (g, t): row g (e < 2) or g + 8, key n_base + 8j + 2t + (e & 1)
+        const bool need_mask = n_base + CHUNK > lim_all;
+        float p0[8], p1[8];
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int n = n_base + 8 * j + 2 * t + e;
+            p0[2 * j + e] = (!need_mask || n < lim0) ? score(sacc[j][e], ch0, cl0) : -INFINITY;
+            mx0 = fmaxf(mx0, p0[2 * j + e]);
+            if (ROWS16) {
+              p1[2 * j + e] = (!need_mask || n < lim1) ? score(sacc[j][2 + e], ch1, cl1) : -INFINITY;
+              mx1 = fmaxf(mx1, p1[2 * j + e]);
+            }
+          }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        const float mn0 = fmaxf(m0, mx0), nb0 = -mn0 * LOG2E;
+        // m0 == mn0 also covers the "nothing seen yet" sentinel, where the fma below would see -1e30 * LOG2E cancel badly
+        const float al0 = (m0 == mn0) ? 1.f : ex2(fmaf(m0, LOG2E, nb0));
+        // the tile maximum of P is pexp(mx): the same instructions compute every P below, and they are monotonic
+        const float ps0 = fmaxf(ex2(fmaf(mx0, LOG2E, nb0)) * (1.f / 127.f), 1e-30f);
+        const float ri0 = __frcp_rn(ps0);
+        int q0[8], qs0 = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          q0[k] = min(__float2int_rn(ex2(fmaf(p0[k], LOG2E, nb0)) * ri0), 127);
+          qs0 += q0[k];
+        }
+        float al1 = 1.f, ps1 = 0.f;
+        int q1[8], qs1 = 0;
+        if (ROWS16) {
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+          const float mn1 = fmaxf(m1, mx1), nb1 = -mn1 * LOG2E;
+          al1 = (m1 == mn1) ? 1.f : ex2(fmaf(m1, LOG2E, nb1));
+          ps1 = fmaxf(ex2(fmaf(mx1, LOG2E, nb1)) * (1.f / 127.f), 1e-30f);
+          const float ri1 = __frcp_rn(ps1);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            q1[k] = min(__float2int_rn(ex2(fmaf(p1[k], LOG2E, nb1)) * ri1), 127);
+            qs1 += q1[k];
+          }
+          m1 = mn1;
+          qs0 |= qs1 << 16;  // both row sums (each < 2^13) through one pair of shuffles
+        }
+        m0 = mn0;
+        qs0 += __shfl_xor_sync(0xffffffffu, qs0, 1);
+        qs0 += __shfl_xor_sync(0xffffffffu, qs0, 2);
+        if (ROWS16) {
+          l1 = l1 * al1 + static_cast<float>(qs0 >> 16) * ps1;
+          qs0 &= 0xffff;
+        }
+        l0 = l0 * al0 + static_cast<float>(qs0) * ps0;
+        // P as the A operand of the PV mma: k slots 4t..4t+3 <- keys {2t, 2t+1, 8+2t, 9+2t}, slots 16+.. <- +16
+        uint32_t pa[4];
+        pa[0] = pack4(q0[0], q0[1], q0[2], q0[3]);
+        pa[2] = pack4(q0[4], q0[5], q0[6], q0[7]);
+        pa[1] = ROWS16 ? pack4(q1[0], q1[1], q1[2], q1[3]) : 0u;
+        pa[3] = ROWS16 ? pack4(q1[4], q1[5], q1[6], q1[7]) : 0u;
+
+        // O += P.V: 16 channels (two n-tiles) per transposing ldmatrix
+#pragma unroll
+        for (int jp = 0; jp < NT / 2; ++jp) {
+          uint32_t b[4];
+          ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp));
+#pragma unroll
+          for (int h2 = 0; h2 < 2; ++h2) {
+            int pacc[4] = {0, 0, 0, 0};
+            mma_s8(pacc, pa, b[h2], b[2 + h2]);
+            float* o = acc[2 * jp + h2];
+            o[0] = o[0] * al0 + static_cast<float>(pacc[0]) * ps0;
+            o[1] = o[1] * al0 + static_cast<float>(pacc[1]) * ps0;
+            if (ROWS16) {
+              o[2] = o[2] * al1 + static_cast<float>(pacc[2]) * ps1;
+              o[3] = o[3] * al1 + static_cast<float>(pacc[3]) * ps1;
+            }
+          }
+        }
+        __syncwarp();  // every lane is done with this stage before lane 0 refills it
+      }
+      gbase += nw > 0 ? nw : 0;
+      if (!ok) atomicExch(a.hdr, 1);
+
+      // -- combine the warps: weights exp2(m_w - M) --
+      if (t == 0) {
+        s_m[warp * 16 + g] = m0, s_l[warp * 16 + g] = l0;
+        s_m[warp * 16 + g + 8] = m1, s_l[warp * 16 + g + 8] = l1;
+      }
+      __syncthreads();  // also: every warp has left the ring, which s_acc aliases
+      {
+        float M0 = -1e30f, M1 = -1e30f;
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) M0 = fmaxf(M0, s_m[w * 16 + g]), M1 = fmaxf(M1, s_m[w * 16 + g + 8]);
+        const float w0 = ex2((m0 - M0) * LOG2E), w1 = ex2((m1 - M1) * LOG2E);
+        float* dst0 = s_acc + (warp * NROWS + g) * ACC_RS + 2 * t;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          *reinterpret_cast<float2*>(dst0 + 8 * j) = make_float2(acc[j][0] * w0, acc[j][1] * w0);
+          if (ROWS16)
+            *reinterpret_cast<float2*>(dst0 + 8 * ACC_RS + 8 * j) =
+                make_float2(acc[j][ROWS16 ? 2 : 0] * w1, acc[j][ROWS16 ? 3 : 1] * w1);
+        }
+        if (tid < 16) {
+          float Mr = -1e30f, Lr = 0.f;
+#pragma unroll
+          for (int w = 0; w < NWARPS; ++w) Mr = fmaxf(Mr, s_m[w * 16 + tid]);
+#pragma unroll
+          for (int w = 0; w < NWARPS; ++w) Lr += s_l[w * 16 + tid] * ex2((s_m[w * 16 + tid] - Mr) * LOG2E);
+          s_M[tid] = Mr;
+          s_inv[tid] = whole ? 1.f / fmaxf(Lr, 1e-30f) : Lr;
+        }
+      }
+      __syncthreads();
+
+      // -- epilogue: 4 channels per thread and step; s_v applied here --
+      const int slot = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * PART_ROWS;
+      for (int i = tid; i < NROWS * (D / 4); i += NTHREADS) {
+        const int row = i / (D / 4), c4 = (i - row * (D / 4)) * 4;
+        const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+        if (rt >= qlen) continue;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int w = 0; w < NWARPS; ++w) {
+          const float4 x = *reinterpret_cast<const float4*>(s_acc + (w * NROWS + row) * ACC_RS + c4);
+          v.x += x.x, v.y += x.y, v.z += x.z, v.w += x.w;
+        }
+        float4 sv4;
+        if (a.pc_v) {
+          sv4 = __ldg(reinterpret_cast<const float4*>(a.vs + kvh * D + c4));
+        } else {
+          const float one = __ldg(a.vs + kvh);
+          sv4 = make_float4(one, one, one, one);
+        }
+        if (whole) {
+          const float inv = s_inv[row];
+          const uint2 o = make_uint2(pack_bf16x2(v.x * inv * sv4.x, v.y * inv * sv4.y),
+                                     pack_bf16x2(v.z * inv * sv4.z, v.w * inv * sv4.w));
+          *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + c4) = o;
+        } else {
+          *reinterpret_cast<float4*>(a.part_acc + static_cast<int64_t>(slot + row) * D + c4) =
+              make_float4(v.x * sv4.x, v.y * sv4.y, v.z * sv4.z, v.w * sv4.w);
+          if (c4 == 0) {
+            a.part_ml[(slot + row) * 2] = s_M[row];
+            a.part_ml[(slot + row) * 2 + 1] = s_inv[row];
+          }
+        }
+      }
+      // generic-proxy writes to the ring (s_acc) come before the next item's TMA writes
+      fence_proxy_async();
+      __syncthreads();
+      u += c1 - c0;
+      first_seg = false;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// merge of items that were cut across CTAs
+// ------------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(D) merge_kernel(const DecodeArgs a, int mtiles_max) {
+  const int req = blockIdx.x, kvh = blockIdx.y / mtiles_max, mt = blockIdx.y - kvh * mtiles_max;
+  const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok;
+  int nchunks, mtiles;
+  if (units_of(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, nchunks, mtiles) == 0 || mt >= mtiles) return;
+  const int W = a.hdr[2];
+  const int A = a.prefix[req] + (kvh * mtiles + mt) * nchunks, B = A + nchunks;
+  const int c_lo = A / W, c_hi = (B - 1) / W;
+  if (c_lo == c_hi) return;  // the item was finished by one CTA
+  const int d = threadIdx.x;
+  for (int row = 0; row < PART_ROWS; ++row) {
+    const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+    if (rt >= qlen) break;
+    // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
+    auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * PART_ROWS + row; };
+    float M = -1e30f;
+    for (int c = c_lo; c <= c_hi; ++c) M = fmaxf(M, a.part_ml[slot_of(c) * 2]);
+    float num = 0.f, den = 0.f;
+    for (int c = c_lo; c <= c_hi; ++c) {
+      const int s = slot_of(c);
+      const float w = ex2((a.part_ml[s * 2] - M) * LOG2E);
+      den += w * a.part_ml[s * 2 + 1];
+      num += w * a.part_acc[static_cast<int64_t>(s) * D + d];
+    }
+    a.out[(tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + d] = __float2bfloat16_rn(num / fmaxf(den, 1e-30f));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceInfo {
+  bool ready = false;
+  int sms = 0;
+  int occ[2][2] = {{0, 0}, {0, 0}};  // [D == 128][ROWS16] resident CTAs per SM
+};
+
+std::mutex g_mu;
+DeviceInfo g_dev[64];
+EncodeFn g_encode = nullptr;
+
+struct MapKey {
+  const void* ptr;
+  int64_t nb, sb, sn, sh;
+  int bs, H, D;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && nb == o.nb && sb == o.sb && sn == o.sn && sh == o.sh && bs == o.bs && H == o.H && D == o.D;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+  int pos[3];
+};
+std::vector<MapEntry> g_maps;
+
+template <int D, bool R16>
+int prepare_variant(int& occ) {
+  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D>::SMEM));
+  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel<D, R16>, NTHREADS, Geom<D>::SMEM));
+  occ = std::max(1, std::min(occ, MAX_CTAS_PER_SM));
+  return KVQ_OK;
+}
+
+int device_info(DeviceInfo** out) {
+  int dev = 0;
+  KVQ_CUDA(cudaGetDevice(&dev));
+  KVQ_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceInfo& di = g_dev[dev];
+  if (!di.ready) {
+    KVQ_CUDA(cudaDeviceGetAttribute(&di.sms, cudaDevAttrMultiProcessorCount, dev));
+    int rc;
+    if ((rc = prepare_variant<64, false>(di.occ[0][0])) != KVQ_OK) return rc;
+    if ((rc = prepare_variant<64, true>(di.occ[0][1])) != KVQ_OK) return rc;
+    if ((rc = prepare_variant<128, false>(di.occ[1][0])) != KVQ_OK) return rc;
+    if ((rc = prepare_variant<128, true>(di.occ[1][1])) != KVQ_OK) return rc;
+    if (!g_encode) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult qres;
+      KVQ_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+      if (qres != cudaDriverEntryPointSuccess || !fn) {
+        set_error("cuTensorMapEncodeTiled is not available from this driver");
+        return KVQ_ERR_CUDA;
+      }
+      g_encode = reinterpret_cast<EncodeFn>(fn);
+    }
+    di.ready = true;
+  }
+  *out = &di;
+  return KVQ_OK;
+}
+
+// Tensor map over a cache view [nb, bs, H, D] (int8). TMA wants ascending-friendly dims; the three outer dims are
+// ordered by stride and pos[] tells the kernel which coordinate slot holds (slot-in-block, head, block).
+int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t sb, int64_t sn, int64_t sh,
+                     CUtensorMap* map, int* pos) {
+  const MapKey key{ptr, nb, sb, sn, sh, bs, H, D};
+  std::lock_guard<std::mutex> lock(g_mu);
+  for (const MapEntry& e : g_maps)
+    if (e.key == key) {
+      *map = e.map;
+      pos[0] = e.pos[0], pos[1] = e.pos[1], pos[2] = e.pos[2];
+      return KVQ_OK;
+    }
+  struct Dim {
+    int which;  // 0 slot-in-block, 1 head, 2 block
+    uint64_t size, stride;
+    uint32_t box;
+  } dims[3] = {{0, static_cast<uint64_t>(bs), static_cast<uint64_t>(sn), 16u},
+               {1, static_cast<uint64_t>(H), static_cast<uint64_t>(sh), 1u},
+               {2, static_cast<uint64_t>(nb), static_cast<uint64_t>(sb), 1u}};
+  for (Dim& d : dims)
+    if (d.size == 1) d.stride = static_cast<uint64_t>(D);  // the stride of a size-1 dim is never used
+  for (int i = 0; i < 3; ++i)
+    for (int j = i + 1; j < 3; ++j)
+      if (dims[j].stride < dims[i].stride) std::swap(dims[i], dims[j]);
+  cuuint64_t gdim[4] = {static_cast<cuuint64_t>(D), dims[0].size, dims[1].size, dims[2].size};
+  cuuint64_t gstr[3] = {dims[0].stride, dims[1].stride, dims[2].stride};
+  cuuint32_t box[4] = {static_cast<cuuint32_t>(D), dims[0].box, dims[1].box, dims[2].box};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  MapEntry e;
+  e.key = key;
+  const CUresult r = g_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), gdim, gstr, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (cache strides %lld/%lld/%lld)", static_cast<int>(r),
+              static_cast<long long>(sb), static_cast<long long>(sn), static_cast<long long>(sh));
+    return KVQ_ERR_CUDA;
+  }
+  for (int i = 0; i < 3; ++i) e.pos[dims[i].which] = i + 1;
+  if (g_maps.size() >= 256) g_maps.clear();
+  g_maps.push_back(e);
+  *map = e.map;
+  pos[0] = e.pos[0], pos[1] = e.pos[1], pos[2] = e.pos[2];
+  return KVQ_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct WorkspaceLayout {
+  size_t prefix, part_acc, part_ml, total;
+};
+WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas) {
+  WorkspaceLayout w;
+  w.prefix = HDR_BYTES;
+  w.part_acc = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
+  w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * PART_ROWS * D * 4;
+  w.total = w.part_ml + static_cast<size_t>(max_ctas) * 2 * PART_ROWS * 2 * 4;
+  return w;
+}
+
+}  // namespace
+}  // namespace kvq
+
+using namespace kvq;
+
+extern "C" __attribute__((visibility("default"))) size_t kvq_decode_workspace_size(int num_seqs, int head_dim) {
+  DeviceInfo* di = nullptr;
+  if (num_seqs < 0 || (head_dim != 64 && head_dim != 128) || device_info(&di) != KVQ_OK) return 0;
+  return workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM).total;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream) {
+  KVQ_REQUIRE(workspace && status, "decode_status: null pointer");
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  KVQ_CUDA(cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  KVQ_CUDA(cudaStreamSynchronize(s));
+  return KVQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         const int32_t* cu_q, const int32_t* seq_lens, const int32_t* block_table,
+                                         const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+                                         int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                         int64_t num_blocks, int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t,
+                                         int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
+                                         int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+                                         int k_per_channel, int v_per_channel, int max_query_len, int qmax,
+                                         void* workspace, size_t workspace_bytes, kvq_stream_t stream) {
+  KVQ_REQUIRE(head_dim == 64 || head_dim == 128, "head_dim must be 64 or 128, got %d", head_dim);
+  KVQ_REQUIRE(block_size >= 16 && (block_size & (block_size - 1)) == 0, "block_size must be a power of two >= 16");
+  KVQ_REQUIRE(num_kv_heads > 0 && num_q_heads > 0 && num_q_heads % num_kv_heads == 0, "bad head counts %d/%d",
+              num_q_heads, num_kv_heads);
+  KVQ_REQUIRE(qmax >= 1 && qmax <= 8, "qmax must be in [1, 8], got %d", qmax);
+  KVQ_REQUIRE(num_seqs >= 0 && num_blocks > 0, "bad sizes");
+  if (num_seqs == 0) return KVQ_OK;
+  KVQ_REQUIRE(q && k_cache && v_cache && out && cu_q && seq_lens && block_table && k_scale && v_scale, "null pointer");
+  KVQ_REQUIRE(aligned16(q) && aligned16(out) && q_stride_t % 8 == 0 && q_stride_h % 8 == 0 && o_stride_t % 8 == 0 &&
+                  o_stride_h % 8 == 0,
+              "q/out rows must be 16-byte aligned");
+  KVQ_REQUIRE(aligned16(k_cache) && aligned16(v_cache) && kc_stride_b % 16 == 0 && kc_stride_n % 16 == 0 &&
+                  kc_stride_h % 16 == 0 && vc_stride_b % 16 == 0 && vc_stride_n % 16 == 0 && vc_stride_h % 16 == 0,
+              "cache rows must be 16-byte aligned");
+  KVQ_REQUIRE(aligned16(k_scale) && aligned16(v_scale), "scales must be 16-byte aligned");
+  DeviceInfo* di = nullptr;
+  int rc = device_info(&di);
+  if (rc != KVQ_OK) return rc;
+
+  const int G = num_q_heads / num_kv_heads;
+  const int max_q = std::max(1, std::min(max_query_len, qmax));
+  const int mtiles_max = (G * max_q + 15) / 16;
+  const bool rows16 = G * max_q > 8;
+  const int occ = di->occ[head_dim == 128][rows16];
+  const int grid = di->sms * occ;
+  const WorkspaceLayout wl = workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM);
+  if (!workspace || workspace_bytes < wl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
+    set_error("decode workspace: need %zu bytes aligned to 256, got %zu at %p", wl.total, workspace_bytes, workspace);
+    return KVQ_ERR_WORKSPACE;
+  }
+
+  DecodeArgs a;
+  a.q = static_cast<const __nv_bfloat16*>(q), a.out = static_cast<__nv_bfloat16*>(out);
+  a.cu_q = cu_q, a.seq_lens = seq_lens, a.block_table = block_table, a.ks = k_scale, a.vs = v_scale;
+  auto* ws = static_cast<uint8_t*>(workspace);
+  a.hdr = reinterpret_cast<int32_t*>(ws);
+  a.prefix = reinterpret_cast<const int32_t*>(ws + wl.prefix);
+  a.part_acc = reinterpret_cast<float*>(ws + wl.part_acc);
+  a.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
+  a.sm_scale = softmax_scale;
+  a.num_seqs = num_seqs, a.Hq = num_q_heads, a.Hkv = num_kv_heads, a.G = G, a.qmax = qmax;
+  a.lbs = 0;
+  while ((1 << a.lbs) < block_size) ++a.lbs;
+  a.bs_mask = block_size - 1;
+  a.q_st = q_stride_t, a.q_sh = q_stride_h, a.o_st = o_stride_t, a.o_sh = o_stride_h, a.bt_stride = bt_stride;
+  a.pc_k = k_per_channel, a.pc_v = v_per_channel;
+  CUtensorMap tm_k, tm_v;
+  if ((rc = cache_tensor_map(k_cache, num_blocks, block_size, num_kv_heads, head_dim, kc_stride_b, kc_stride_n,
+                             kc_stride_h, &tm_k, a.kpos)) != KVQ_OK)
+    return rc;
+  if ((rc = cache_tensor_map(v_cache, num_blocks, block_size, num_kv_heads, head_dim, vc_stride_b, vc_stride_n,
+                             vc_stride_h, &tm_v, a.vpos)) != KVQ_OK)
+    return rc;
+
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grid, a.hdr,
+                                reinterpret_cast<int32_t*>(ws + wl.prefix));
+  if (head_dim == 128) {
+    if (rows16)
+      decode_kernel<128, true><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
+    else
+      decode_kernel<128, false><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
+    merge_kernel<128><<<dim3(num_seqs, num_kv_heads * mtiles_max), 128, 0, s>>>(a, mtiles_max);
+  } else {
+    if (rows16)
+      decode_kernel<64, true><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
+    else
+      decode_kernel<64, false><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
+    merge_kernel<64><<<dim3(num_seqs, num_kv_heads * mtiles_max), 64, 0, s>>>(a, mtiles_max);
+  }
+  KVQ_CUDA(cudaGetLastError());
+  return KVQ_OK;
+}

@@ -1,0 +1,56 @@
+"""Helpers for the GPU parity tests: move seeded CPU cases to the device, call the kernels through the
+C ABI (via the kvq_b200 host layer), run the CPU oracle on the same bytes."""
+import numpy as np
+import torch
+
+from kvq_b200 import cuda_kernels as ck
+from oracle import kvq_oracle as orc
+
+DEV = "cuda"
+
+
+def to_dev(static):
+    return {k: v.to(DEV) for k, v in static.items()}
+
+
+def run_decode(case, max_query_len=None, out=None, interleaved=False, device_case=None):
+    """decode_attention on the case's int8 cache; returns the bf16 output as a CPU float32 array.
+    interleaved=True stores K and V in one [nb, bs, H, 2D] tensor (vLLM's layout) and passes strided views."""
+    q = case["q"].to(DEV)
+    if interleaved:
+        kv = torch.cat([case["kq"], case["vq"]], dim=-1).to(DEV)
+        kq, vq = kv.split(case["kq"].shape[-1], dim=-1)
+    else:
+        kq, vq = case["kq"].to(DEV), case["vq"].to(DEV)
+    out = torch.zeros_like(q) if out is None else out
+    mql = max_query_len if max_query_len is not None else max(case["q_lens"])
+    ck.decode_attention(q, kq, vq, out, case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV),
+                        case["block_table"].to(DEV), case["softmax_scale"], to_dev(case["static"]), max_query_len=mql)
+    torch.cuda.synchronize()
+    assert ck.decode_status() == 0, "a bounded wait inside the attention kernel expired"
+    return out.float().cpu().numpy()
+
+
+def oracle_attention(case, requests=None, short_q=8):
+    st = case["static"]
+    return orc.paged_static_attention(case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(),
+                                      case["cu_seqlens_q"].numpy(), case["seq_lens"].numpy(),
+                                      case["block_table"].numpy(), case["softmax_scale"], st["k_scale"].numpy(),
+                                      st["v_scale"].numpy(), short_q=short_q, p_tile=32, requests=requests)
+
+
+def short_row_mask(case, limit=8):
+    """True for query rows of requests the INT8 kernel handles (1 <= q_len <= limit)."""
+    q_lens = np.asarray(case["q_lens"])
+    return np.repeat((q_lens >= 1) & (q_lens <= limit), q_lens)
+
+
+def fixture_case(fx):
+    """A golden .npz with stored inputs -> the dict layout workloads.paged_case returns."""
+    cu = fx["cu_seqlens_q"]
+    return {"q": torch.from_numpy(fx["q"].view(np.int16)).view(torch.bfloat16), "kq": torch.from_numpy(fx["kq"]),
+            "vq": torch.from_numpy(fx["vq"]), "cu_seqlens_q": torch.from_numpy(cu),
+            "seq_lens": torch.from_numpy(fx["seq_lens"]), "block_table": torch.from_numpy(fx["block_table"]),
+            "static": {"k_scale": torch.from_numpy(fx["k_scale"]), "v_scale": torch.from_numpy(fx["v_scale"]),
+                       "k_mu": torch.from_numpy(fx["k_mu"])},
+            "softmax_scale": float(fx["softmax_scale"]), "q_lens": np.diff(cu).tolist()}

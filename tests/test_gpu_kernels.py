@@ -1,0 +1,274 @@
+"""GPU parity tests: the sm_100a kernels, called through the C ABI, against the CPU oracle and the golden
+fixtures made by the reference's own code.
+
+Bars: cache bytes, quantized q and dequantized pages bit-exact; attention output within max-abs 1e-2 and
+mean-abs 1e-3 of the fp32 oracle (the reference's own kernel test uses rel_l2 < 5e-3, checked too)."""
+import numpy as np
+import pytest
+import torch
+from conftest import load_golden
+from gpu_util import DEV, fixture_case, oracle_attention, run_decode, short_row_mask, to_dev
+
+from kvq_b200 import cuda_kernels as ck
+from kvq_b200 import workloads
+from oracle import kvq_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS, MEAN_ABS, REL_L2 = 1e-2, 1e-3, 5e-3
+
+DECODE = ([1] * 11, [1, 16, 17, 31, 32, 33, 250, 1023, 2049, 700, 3100])
+SHORT = ([2, 4, 8, 3, 1, 5, 7, 1, 6], [37, 650, 1025, 9, 2050, 100, 2800, 16, 513])
+MIXED = ([1, 1, 7, 40, 130, 1, 290, 9, 4, 0], [590, 33, 7, 480, 130, 1400, 910, 1900, 70, 12])
+
+
+def assert_close(ref, out, what="", strict=False):
+    """ref: fp32 oracle / reference output; out: the kernel's bf16 output widened to fp32.
+    strict: max-abs 1e-2 and mean-abs 1e-3 outright (the benchmark configurations, whose outputs are averages
+    over long contexts). Otherwise the rounding of the bf16 store itself (half an ulp, <= 2^-8 |ref|) is allowed
+    on top: short-context edge cases have outputs of magnitude 2..8, where one bf16 ulp is already 0.016..0.03."""
+    err = orc.compare(ref, out)
+    d = np.abs(np.asarray(ref, np.float64) - np.asarray(out, np.float64))
+    slack = 0.0 if strict else np.abs(ref) * 2.0 ** -8
+    assert (d <= MAX_ABS + slack).all(), (what, err)
+    assert err["mean_abs"] < MEAN_ABS + (0.0 if strict else float(np.mean(slack)) / 2) and err["rel_l2"] < REL_L2, (what, err)
+    return err
+
+
+def bf16_t(bits):
+    return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------------------------------
+# fused quantize + cache write, page dequantization
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("gran", ["channel", "head"])
+@pytest.mark.parametrize("layout", ["interleaved", "separate"])
+def test_quant_cache_golden(d, gran, layout):
+    """Reference-generated fixture: 200 tokens + 8 padded rows, every 17th slot -1, both cache layouts."""
+    fx = load_golden(f"write_d{d}_{gran}.npz")
+    key, value = bf16_t(fx["key"]).to(DEV), bf16_t(fx["value"]).to(DEV)
+    nb, bs, H = fx["k_cache"].shape[:3]
+    if layout == "interleaved":   # vLLM 0.32 logical [nb, H, bs, 2D] over physical [nb, bs, H, 2D]
+        kv = torch.zeros(nb, bs, H, 2 * d, dtype=torch.int8, device=DEV)
+        kc, vc = kv.split(d, dim=-1)
+    else:
+        kc = torch.zeros(nb, bs, H, d, dtype=torch.int8, device=DEV)
+        vc = torch.zeros_like(kc)
+    st = to_dev({k: torch.from_numpy(fx[k]) for k in ("k_scale", "v_scale", "k_mu")})
+    ck.quant_reshape_and_cache(key, value, kc, vc, torch.from_numpy(fx["slots"]).to(DEV), st)
+    assert np.array_equal(kc.cpu().numpy(), fx["k_cache"]) and np.array_equal(vc.cpu().numpy(), fx["v_cache"])
+    # dequantize all pages through an identity table: bit-exact bf16
+    ko = torch.empty(nb, bs, H, d, dtype=torch.bfloat16, device=DEV)
+    vo = torch.empty_like(ko)
+    ident = torch.arange(nb, dtype=torch.int32, device=DEV)
+    ck.dequant_pages(kc, vc, ko, vo, ident[None].contiguous(), torch.zeros_like(ident), ident, st)
+    assert np.array_equal(ko.cpu().view(torch.int16).numpy().view(np.uint16), fx["k_dequant"])
+    assert np.array_equal(vo.cpu().view(torch.int16).numpy().view(np.uint16), fx["v_dequant"])
+
+
+def test_quant_cache_config1_round_trip():
+    """BASELINE config 1: 8192 tokens into a 65536-slot cache, bit-exact against the oracle, then the pages
+    dequantized back to bf16 (also bit-exact). A strided key (fused qkv row stride) is used."""
+    c = workloads.config1()
+    st, bs, nb = c["static"], c["block_size"], c["num_blocks"]
+    T, H, D = c["key"].shape
+    qkv = torch.zeros(T, 3 * H * D + 64, dtype=torch.bfloat16, device=DEV)
+    key = qkv[:, H * D:2 * H * D].view(T, H, D)
+    value = qkv[:, 2 * H * D:3 * H * D].view(T, H, D)
+    key.copy_(c["key"]), value.copy_(c["value"])
+    kc = torch.zeros(nb, bs, H, D, dtype=torch.int8, device=DEV)
+    vc = torch.zeros_like(kc)
+    ck.quant_reshape_and_cache(key, value, kc, vc, c["slots"].to(DEV), to_dev(st))
+    ref_k, ref_v = np.zeros((nb, bs, H, D), np.int8), np.zeros((nb, bs, H, D), np.int8)
+    orc.quant_cache_write(c["key"].float().numpy(), c["value"].float().numpy(), ref_k, ref_v, c["slots"].numpy(),
+                          st["k_scale"].numpy(), st["v_scale"].numpy(), st["k_mu"].numpy())
+    assert np.array_equal(kc.cpu().numpy(), ref_k) and np.array_equal(vc.cpu().numpy(), ref_v)
+    # pages that hold the tokens, in slot order
+    pages = torch.unique(c["slots"] // bs).to(torch.int32)
+    P = pages.numel()
+    ko = torch.empty(P, bs, H, D, dtype=torch.bfloat16, device=DEV)
+    vo = torch.empty_like(ko)
+    idx = torch.arange(P, dtype=torch.int32, device=DEV)
+    ck.dequant_pages(kc, vc, ko, vo, pages[None].contiguous().to(DEV), torch.zeros_like(idx), idx, to_dev(st))
+    rk, rv = orc.dequant_pages(ref_k, ref_v, pages[None].numpy(), np.zeros(P, np.int32), np.arange(P, dtype=np.int32),
+                               st["k_scale"].numpy(), st["v_scale"].numpy())
+    assert np.array_equal(ko.float().cpu().numpy(), rk) and np.array_equal(vo.float().cpu().numpy(), rv)
+
+
+def test_quant_cache_all_padding_and_empty():
+    c = workloads.write_case(3, 64, 4, 128, num_blocks=8)
+    kc = torch.zeros(8, 16, 4, 128, dtype=torch.int8, device=DEV)
+    vc = torch.zeros_like(kc)
+    slots = torch.full((64,), -1, dtype=torch.int64, device=DEV)
+    ck.quant_reshape_and_cache(c["key"].to(DEV), c["value"].to(DEV), kc, vc, slots, to_dev(c["static"]))
+    assert not kc.any() and not vc.any()
+    slots[:10] = torch.arange(10, device=DEV) * 3
+    ck.quant_reshape_and_cache(c["key"].to(DEV), c["value"].to(DEV), kc, vc, slots, to_dev(c["static"]))
+    assert int((kc != 0).flatten(2).any(-1).sum()) == 10
+    ck.quant_reshape_and_cache(c["key"].to(DEV), c["value"].to(DEV), kc, vc, slots[:0], to_dev(c["static"]))  # no tokens
+
+
+def test_layout_violations_raise():
+    c = workloads.write_case(3, 8, 4, 128, num_blocks=2)
+    kc = torch.zeros(2, 16, 4, 128, dtype=torch.int8, device=DEV)
+    with pytest.raises(RuntimeError):   # cache with a strided last dim
+        ck.quant_reshape_and_cache(c["key"].to(DEV), c["value"].to(DEV), kc.transpose(2, 3), kc, c["slots"].to(DEV),
+                                   to_dev(c["static"]))
+    with pytest.raises(RuntimeError):   # head_dim 96 is not supported
+        ck.quant_q(torch.zeros(4, 8, 96, dtype=torch.bfloat16, device=DEV), torch.ones(2, 96, device=DEV))
+
+
+# ---------------------------------------------------------------------------------------------------
+# q quantization
+# ---------------------------------------------------------------------------------------------------
+def test_quant_q_golden():
+    fx = load_golden("quant_q.npz")
+    q = bf16_t(fx["q"]).to(DEV)
+    ks = torch.from_numpy(fx["k_scale"]).to(DEV)
+    for group in (128, 32):
+        qi, qs = ck.quant_q(q, ks, group)
+        assert np.array_equal(qi.cpu().numpy(), fx[f"q_i8_g{group}"])
+        assert np.array_equal(qs.cpu().numpy(), fx[f"q_scale_g{group}"])
+    qi, qs = ck.quant_q(q, torch.ones(4, 1, device=DEV))
+    assert np.array_equal(qi.cpu().numpy(), fx["q_i8_per_head"])
+    assert np.array_equal(qs.cpu().numpy(), fx["q_scale_per_head"])
+
+
+def test_quant_q_strided_rows_vs_oracle():
+    g = torch.Generator().manual_seed(5)
+    T = 2048 + 3
+    qkv = (torch.randn(T, 40, 128, generator=g) * 3).to(torch.bfloat16)
+    q = qkv[:, :28].to(DEV)                      # contiguous copy
+    q_strided = qkv.to(DEV)[:, :28]              # token stride 40 * 128
+    ks = (torch.rand(4, 128, generator=g) + 0.01)
+    ri, rs = orc.quant_q(qkv[:, :28].float().numpy(), ks.numpy(), 128)
+    for t in (q, q_strided):
+        qi, qs = ck.quant_q(t, ks.to(DEV))
+        assert np.array_equal(qi.cpu().numpy(), ri) and np.array_equal(qs.cpu().numpy(), rs)
+
+
+# ---------------------------------------------------------------------------------------------------
+# INT8 attention
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["attn_short_smooth.npz", "attn_per_head_d64.npz"])
+def test_attention_golden(name):
+    """Against outputs of the reference's implementation B itself (tests/golden)."""
+    fx = load_golden(name)
+    out = run_decode(fixture_case(fx))
+    assert_close(fx["ref_out"], out, name)
+
+
+def test_attention_config0_golden():
+    """BASELINE config 0 (4 requests, contexts 128..512): reference output, then the bf16 golden within the
+    reference's own quantization tolerance."""
+    fx = load_golden("attn_config0.npz")
+    out = run_decode(workloads.config0())
+    assert_close(fx["ref_out"], out, "config0", strict=True)
+    assert orc.compare(fx["bf16_golden"], out)["rel_l2"] < 0.05
+
+
+def test_mixed_batch_leaves_long_requests_alone():
+    fx = load_golden("attn_mixed_long.npz")
+    case = fixture_case(fx)
+    out = torch.full_like(case["q"], 7.0).to(DEV)
+    got = run_decode(case, out=out)
+    short = short_row_mask(case)
+    assert (got[~short] == 7.0).all() and not (got[short] == 7.0).all(-1).all(-1).any()
+    assert_close(fx["ref_out"][short], got[short], "mixed short rows")
+
+
+@pytest.mark.parametrize("shape", [(28, 4, 128), (12, 2, 128), (32, 8, 128), (16, 1, 128), (14, 2, 64), (16, 4, 64)])
+@pytest.mark.parametrize("batch", ["decode", "short"])
+@pytest.mark.parametrize("variant", ["per_channel", "per_head", "interleaved"])
+def test_short_queries_match_oracle(shape, batch, variant):
+    """Decode and short multi-token queries (causal inside the request, several m tiles when q_len * G > 16),
+    head_dim 128 and 64, per-channel and per-head scales, smooth-K, both cache layouts."""
+    hq, hkv, d = shape
+    q_lens, seq_lens = DECODE if batch == "decode" else SHORT
+    case = workloads.paged_case(100 + hq + d, hq, hkv, d, q_lens, seq_lens, per_channel=variant != "per_head",
+                                smooth=True, q_std=3.0)
+    out = run_decode(case, interleaved=variant == "interleaved")
+    assert_close(oracle_attention(case), out, (shape, batch, variant))
+
+
+def test_mixed_lengths_and_padding_requests():
+    case = workloads.paged_case(9, 28, 4, 128, *MIXED, q_std=3.0)
+    out = torch.full_like(case["q"], 7.0).to(DEV)
+    got = run_decode(case, out=out)
+    short = short_row_mask(case)
+    assert (got[~short] == 7.0).all()
+    assert_close(oracle_attention(case)[short], got[short], "mixed")
+
+
+@pytest.mark.parametrize("block_size", [32, 64, 128])
+def test_larger_pages(block_size):
+    case = workloads.paged_case(31, 28, 4, 128, [1, 3, 1, 8], [100, 777, 2048, 333], block_size=block_size)
+    assert_close(oracle_attention(case), run_decode(case), block_size)
+
+
+def test_wider_tables_and_extra_rows():
+    """vLLM hands tables wider than the request and seq_lens/block_table with more rows than requests."""
+    case = workloads.paged_case(32, 28, 4, 128, [1, 5, 1], [300, 90, 1000])
+    ref = oracle_attention(case)
+    bt = case["block_table"]
+    case["block_table"] = torch.cat([torch.cat([bt, bt[:, :1].expand(-1, 5)], 1), bt.new_zeros(2, bt.shape[1] + 5)], 0)
+    case["seq_lens"] = torch.cat([case["seq_lens"], case["seq_lens"].new_zeros(2)])
+    assert_close(ref, run_decode(case), "wide table")
+
+
+def test_single_long_request_is_split_over_many_ctas():
+    """One request with a 20k context: every (kv head) item is cut across dozens of CTAs and merged."""
+    case = workloads.paged_case(33, 28, 4, 128, [1], [20000])
+    assert_close(oracle_attention(case), run_decode(case), "split")
+    case = workloads.paged_case(34, 28, 4, 128, [6], [9000])
+    assert_close(oracle_attention(case), run_decode(case), "split short-q")
+
+
+def test_headline_shape_subset_vs_oracle():
+    """Full-size contexts (32768) at a batch the oracle finishes in seconds; the decode kernel sees 8 requests."""
+    case = workloads.paged_case(35, 28, 4, 128, [1] * 8, [32768] * 8, num_blocks=8 * 2048 + 8)
+    assert_close(oracle_attention(case), run_decode(case), "8x32k", strict=True)
+
+
+def test_cuda_graph_replay_is_bit_identical():
+    """Replay with new inputs equals an eager call: no host-side state, no atomics in the data path."""
+    for q_len in (1, 4, 5):
+        case = workloads.paged_case(40 + q_len, 28, 4, 128, [q_len] * 8, [100, 2000, 37, 512, 1500, 64, 999, 3000],
+                                    q_std=3.0)
+        q, kq, vq = case["q"].to(DEV), case["kq"].to(DEV), case["vq"].to(DEV)
+        cu, sl, bt = case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV), case["block_table"].to(DEV)
+        st = to_dev(case["static"])
+        out = torch.zeros_like(q)
+        fn = lambda o: ck.decode_attention(q, kq, vq, o, cu, sl, bt, case["softmax_scale"], st, max_query_len=q_len)  # noqa: E731
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            fn(out)
+        torch.cuda.current_stream().wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn(out)
+        q2 = workloads.paged_case(77, 28, 4, 128, [q_len] * 8, [100] * 8, q_std=3.0)["q"]
+        q.copy_(q2)
+        sl.sub_(1)          # same shapes, new contents
+        g.replay()
+        ref = fn(torch.zeros_like(q))
+        torch.cuda.synchronize()
+        assert torch.equal(ref, out)
+        # scales are read through their storage: an in-place update reaches the captured graph
+        st["v_scale"].mul_(2)
+        g.replay()
+        ref2 = fn(torch.zeros_like(q))
+        torch.cuda.synchronize()
+        assert torch.equal(ref2, out) and not torch.equal(ref2, ref)
+
+
+def test_check_inputs_reports_bad_pages():
+    case = workloads.paged_case(50, 28, 4, 128, [1, 1], [100, 50])
+    bt = case["block_table"].clone()
+    bt[1, 0] = 10 ** 6
+    with pytest.raises(RuntimeError, match="kvq input check"):
+        ck.check_inputs(case["q"].to(DEV), case["kq"].to(DEV), case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV),
+                        bt.to(DEV), None)

@@ -1,0 +1,319 @@
+"""Benchmark of the INT8 paged decode attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload (per GPU): one attention layer of Qwen2.5-7B geometry (28 q heads, 4 kv heads, head_dim 128, block 16),
+128 requests x 32768 context, q_len 1, int8 K/V with static per-channel scales, pages randomly permuted;
+synthetic seeded data (no dataset or checkpoint involved). A step is one pass of the decode-attention path over
+the batch. The metric is the KV bytes the kernel must read (sum L * Hkv * D * 2) per second, summed over GPUs;
+microseconds per call and decode tokens/s (requests per step / time) are reported beside it.
+Requests are sharded over GPUs (each rank owns its requests and their pages): weak scaling, no collective in
+the data path.
+
+One JSON line is printed by rank 0. `--impl reference` times the CPU restatement of the reference's PyTorch
+implementation B (oracle/) on the host cores instead, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "int8-kvcache_b200"))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+BATCH, CTX = 128, 32768
+HQ, HKV, D, BLOCK = 28, 4, 128, 16
+METRIC = "int8_paged_decode_attention_kv_bandwidth_128x32k"
+UNIT = "GB/s"
+H100_PUBLISHED_GBS = 2439.0   # reference's own kernel, H100, 128 x 32k (docs/tables/kernels_h100.md:53)
+WORKLOAD = f"decode_attention {BATCH}x{CTX} per GPU, Hq{HQ}/Hkv{HKV}/D{D}/block{BLOCK}, q_len 1, int8 KV static per-channel"
+
+
+def kv_bytes(seq_lens):
+    return int(sum(seq_lens)) * HKV * D * 2
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """nvidia-smi in the background during the timed region: SM clock and throttle reasons."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        self.proc.wait()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6:
+                continue
+            try:
+                sm.append(float(parts[0])), mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            reasons.update(n for n, v in zip(names, parts[2:]) if v == "Active")
+        os.unlink(self.file.name)
+        if not sm:
+            return None
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's implementation B on the host cores
+# --------------------------------------------------------------------------------------------------------
+def cpu_sample_case(requests, seed=1002):
+    """`requests` requests of the benchmark workload (same shapes and distributions), generated on the CPU."""
+    from kvq_b200 import workloads
+
+    return workloads.paged_case(seed, HQ, HKV, D, [1] * requests, [CTX] * requests, BLOCK,
+                                num_blocks=requests * (CTX // BLOCK) + 1)
+
+
+def cpu_run(case):
+    from oracle import kvq_oracle as orc
+
+    st = case["static"]
+    args = (case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(), case["cu_seqlens_q"].numpy(),
+            case["seq_lens"].numpy(), case["block_table"].numpy(), case["softmax_scale"], st["k_scale"].numpy(),
+            st["v_scale"].numpy())
+    t0 = time.perf_counter()
+    orc.paged_static_attention(*args, short_q=8, p_tile=32)
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(requests=16, repeats=3):
+    case = cpu_sample_case(requests)
+    cpu_run(case)                                   # warm-up (BLAS thread pool, page faults)
+    t = min(cpu_run(case) for _ in range(repeats))
+    return {"value": kv_bytes([CTX] * requests) / t / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{requests} of the {BATCH} requests (x{CTX} context), numpy port of kvq/int8_ref.py "
+                      f"implementation B, BLAS threads = all cores, best of {repeats}",
+            "seconds_per_sample": t}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    requests = 8
+    case = cpu_sample_case(requests)
+    for _ in range(args.warmup):
+        cpu_run(case)
+    times = [cpu_run(case) for _ in range(args.steps)]
+    t = sum(times) / len(times)
+    value = kv_bytes([CTX] * requests) / t / 1e9
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "sample": f"each step = {requests} of the {BATCH} requests on the host CPU"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+                             "sample": f"{requests} requests x {CTX} context per step; oracle/kvq_oracle.py (numpy "
+                                       "restatement of kvq/int8_ref.py implementation B; the reference is Python and "
+                                       "is not present on the GPU box)"},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------------------
+# GPU arm
+# --------------------------------------------------------------------------------------------------------
+def run_ours(args, rank, world, local_rank):
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from kvq_b200 import _native
+    from kvq_b200 import cuda_kernels as ck
+    from kvq_b200 import workloads
+
+    lib = ck.ext()   # raises if the native library is missing: there is no fallback path
+    batch, ctx = args.batch, args.ctx
+    case = workloads.decode_batch_on_device(batch, ctx, dev, seed=1002 + rank)
+    q, kq, vq, st = case["q"], case["kq"], case["vq"], case["static"]
+    cu, sl, bt = case["cu_seqlens_q"], case["seq_lens"], case["block_table"]
+    scale = case["softmax_scale"]
+    out = torch.empty_like(q)
+    bytes_per_step = kv_bytes(case["seq_lens_list"])
+
+    def step():
+        ck.decode_attention(q, kq, vq, out, cu, sl, bt, scale, st, max_query_len=1)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    warmup = args.warmup if args.profile else max(args.warmup, 3)
+    for _ in range(warmup):
+        step()
+    sync_all()
+    assert ck.decode_status(dev) == 0, "attention kernel reported an expired wait"
+
+    # ---- timed region: K steps, device events; a second pair of events per step brackets the main kernel ----
+    def new_event():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        return e
+
+    k_start = [new_event() for _ in range(args.steps)]
+    k_stop = [new_event() for _ in range(args.steps)]
+    t_start, t_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    t_start.record()
+    for i in range(args.steps):
+        lib.kvq_debug_kernel_events(k_start[i].cuda_event, k_stop[i].cuda_event)
+        step()
+    t_stop.record()
+    sync_all()
+    lib.kvq_debug_kernel_events(None, None)
+    elapsed_ms = t_start.elapsed_time(t_stop)
+    kernel_ms = [a.elapsed_time(b) for a, b in zip(k_start, k_stop)]
+    if sampler is not None and elapsed_ms < 1500 and not args.profile:   # keep the sampler alive long enough to see loaded clocks
+        t_end = time.time() + 1.5
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if sampler is not None else None
+
+    if args.profile:   # profiling runs (ncu): kernel timings only
+        print(json.dumps({"profile_run": True, "batch": batch, "ctx": ctx, "kernel_us": [k * 1e3 for k in kernel_ms],
+                          "GBps": [bytes_per_step / (k * 1e-3) / 1e9 for k in kernel_ms]}), flush=True)
+        return
+    # ---- end to end through the public API with host buffers ----
+    hk = torch.randn(batch, HKV, D).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(batch, HKV, D).to(torch.bfloat16).pin_memory()
+    hq = q.cpu().pin_memory()
+    last = sl.cpu().long() - 1
+    h_slots = (bt.cpu().long()[torch.arange(batch), last // BLOCK] * BLOCK + last % BLOCK).pin_memory()
+    h_cu, h_sl, h_bt = cu.cpu().pin_memory(), sl.cpu().pin_memory(), bt.cpu().pin_memory()
+    h_out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    d_k, d_v, d_slots = hk.to(dev), hv.to(dev), h_slots.to(dev)
+    d_q, d_cu, d_sl, d_bt = torch.empty_like(q), torch.empty_like(cu), torch.empty_like(sl), torch.empty_like(bt)
+    h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, h_slots, h_cu, h_sl, h_bt))
+    d2h = h_out.numel() * h_out.element_size()
+
+    def e2e_step():
+        d_q.copy_(hq, non_blocking=True), d_k.copy_(hk, non_blocking=True), d_v.copy_(hv, non_blocking=True)
+        d_slots.copy_(h_slots, non_blocking=True), d_cu.copy_(h_cu, non_blocking=True)
+        d_sl.copy_(h_sl, non_blocking=True), d_bt.copy_(h_bt, non_blocking=True)
+        ck.quant_reshape_and_cache(d_k, d_v, kq, vq, d_slots, st)
+        ck.paged_attention(d_q, kq, vq, out, d_cu, d_sl, d_bt, 1, scale, st)
+        h_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()      # the caller needs the result on the host
+
+    for _ in range(3):
+        e2e_step()
+    sync_all()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_start.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e_stop.record()
+    sync_all()
+    e2e_ms = e_start.elapsed_time(e_stop)
+
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    ms_per_step = elapsed_ms / args.steps
+    value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    peak, peak_src = peaks()
+    k_ms = float(np.mean(kernel_ms))
+    achieved = bytes_per_step / (k_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": value / H100_PUBLISHED_GBS,
+        "vs_baseline_note": "reference's own CUDA kernel on H100, 2439 GB/s (published; no B200 number exists)",
+        "dtype": "int8 (int32 accumulate), fp32 softmax", "data": "synthetic",
+        "config": {"workload": WORKLOAD if (batch, ctx) == (BATCH, CTX) else f"decode_attention {batch}x{ctx} per GPU (non-headline size)", "global_requests": batch * world, "sharding": f"requests over {world} GPU(s)",
+                   "l2": "inputs (4.3 GB of KV per step) are larger than L2", "timed_call": "cuda_kernels.decode_attention"},
+        "us_per_call": ms_per_step * 1e3, "decode_tok_per_s": batch * world / (ms_per_step * 1e-3),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "decode_kernel<128,false>",
+                     "kernel_us": k_ms * 1e3, "algorithmic_bytes_per_launch": bytes_per_step,
+                     "traffic": TRAFFIC_PER_LAUNCH},
+        "e2e": {"value": world * bytes_per_step / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "us_per_step": e2e_ms / args.steps * 1e3,
+                "path": "pinned host q/new K,V/slots/metadata -> H2D -> quant_reshape_and_cache -> paged_attention -> "
+                        "D2H of the output; the KV cache itself is resident state"},
+        "gpu_launches": args.steps * 3,
+        "clocks": clocks,
+    }
+    if world == 1 and not args.no_cpu:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on this workload, from the ncu capture
+# summarised in profiles/ (None until a capture has been taken).
+TRAFFIC_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU (default: the headline 128)")
+    ap.add_argument("--ctx", type=int, default=CTX, help="context length (default: the headline 32768)")
+    ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local_rank = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        if args.steps == 20 and args.warmup == 5:
+            args.steps, args.warmup = 5, 3
+        run_reference_arm(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU (there is no CPU path for the product arm)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

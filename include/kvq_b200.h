@@ -108,6 +108,14 @@ int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_
 int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream);
 
 /*
+ * Profiling helper: when both arguments are non-null cudaEvent_t handles, every following
+ * kvq_int8_decode_attention call records them on its stream immediately before and after the main attention
+ * kernel (between the plan and merge kernels), so a benchmark can time that kernel alone. Pass nulls to stop.
+ * Process-wide, not thread-safe, not for use under graph capture. No reference counterpart.
+ */
+int kvq_debug_kernel_events(void* start_event, void* stop_event);
+
+/*
  * Dequantize pages of the INT8 cache into a temporary bf16 paged cache for the long-query (prefill) path.
  * Replaces dequant_pages(kc, vc, ko, vo, block_table, src_req, src_j, ks, vs), kvq/cuda/int8_kv.cu:650-672
  * (kernel :511-542). Output page p = bf16(rne(int8 page block_table[src_req[p]][src_j[p]] * scale)), laid out

@@ -710,6 +710,8 @@ int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t 
   return KVQ_OK;
 }
 
+cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;  // optional profiling brackets around decode_kernel
+
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
@@ -809,19 +811,28 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   auto s = reinterpret_cast<cudaStream_t>(stream);
   plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grid, a.hdr,
                                 reinterpret_cast<int32_t*>(ws + wl.prefix));
+  if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   if (head_dim == 128) {
     if (rows16)
       decode_kernel<128, true><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
     else
       decode_kernel<128, false><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
+    if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
     merge_kernel<128><<<dim3(num_seqs, num_kv_heads * mtiles_max), 128, 0, s>>>(a, mtiles_max);
   } else {
     if (rows16)
       decode_kernel<64, true><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
     else
       decode_kernel<64, false><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
+    if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
     merge_kernel<64><<<dim3(num_seqs, num_kv_heads * mtiles_max), 64, 0, s>>>(a, mtiles_max);
   }
   KVQ_CUDA(cudaGetLastError());
+  return KVQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_debug_kernel_events(void* start_event, void* stop_event) {
+  g_ev_start = static_cast<cudaEvent_t>(start_event);
+  g_ev_stop = static_cast<cudaEvent_t>(stop_event);
   return KVQ_OK;
 }

@@ -271,7 +271,8 @@ def run_ours(args, rank, world, local_rank):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "decode_kernel<128,false>",
                      "kernel_us": k_ms * 1e3, "algorithmic_bytes_per_launch": bytes_per_step,
-                     "traffic": TRAFFIC_PER_LAUNCH},
+                     "traffic": TRAFFIC_16X32K * batch // 16 if ctx == CTX else None,
+                     "traffic_source": "ncu capture of 16x32768 scaled by requests (profiles/)"},
         "e2e": {"value": world * bytes_per_step / (e2e_ms / args.steps * 1e-3) / 1e9, "unit": UNIT,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "us_per_step": e2e_ms / args.steps * 1e3,
                 "path": "pinned host q/new K,V/slots/metadata -> H2D -> quant_reshape_and_cache -> paged_attention -> "
@@ -286,9 +287,10 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on this workload, from the ncu capture
-# summarised in profiles/ (None until a capture has been taken).
-TRAFFIC_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu capture summarised in
+# profiles/decode_kernel_16x32k_ncu_full.md: 541,869,312 bytes for 16 requests x 32768 context. Traffic is
+# proportional to the requests (every CTA streams its slice of the KV bytes once), so it is scaled to the batch.
+TRAFFIC_16X32K = 537_539_584 + 4_329_728
 
 
 def main():

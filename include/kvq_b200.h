@@ -108,6 +108,35 @@ int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_
 int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream);
 
 /*
+ * The same attention as kvq_int8_decode_attention for callers that cannot allocate device memory, so they
+ * have no workspace to pass: an engine that gave all free HBM to its KV pool, code running inside another
+ * framework's allocator or graph capture, a latency-critical loop that must never hit cudaMalloc's implicit
+ * synchronization. This entry point has no counterpart in the reference. It allocates nothing (no cudaMalloc,
+ * no cudaFree, no allocating library call): the scratch is a fixed array of kvq_static_workspace_bytes()
+ * (10 MiB) inside the library's device image, resident on every GPU that loads the library until the process
+ * exits. Inputs and outputs are still the caller's.
+ *   - Limit: a batch whose scratch (kvq_decode_workspace_size) exceeds the array is rejected with
+ *     KVQ_ERR_WORKSPACE and a message; nothing is launched. 10 MiB covers GPUs of up to 148 SMs and about
+ *     150,000 requests per call.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and caches it; make that first call outside any stream capture.
+ *   - All calls on a device share the one array, which keeps the previous call's contents. Nothing in it has
+ *     to start at zero (each call rewrites the plan, the status word and every partial result it later reads),
+ *     but two calls that overlap on the GPU (different streams without ordering) race on it.
+ *   - kvq_decode_status does not apply (it needs a workspace pointer).
+ */
+size_t kvq_static_workspace_bytes(void);
+int kvq_int8_decode_attention_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int32_t* cu_q, const int32_t* seq_lens, const int32_t* block_table,
+                                      const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+                                      int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                      int64_t num_blocks, int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t,
+                                      int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
+                                      int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+                                      int k_per_channel, int v_per_channel, int max_query_len, int qmax,
+                                      kvq_stream_t stream);
+
+/*
  * Profiling helper: when both arguments are non-null cudaEvent_t handles, every following
  * kvq_int8_decode_attention call records them on its stream immediately before and after the main attention
  * kernel (between the plan and merge kernels), so a benchmark can time that kernel alone. Pass nulls to stop.

@@ -836,3 +836,69 @@ extern "C" __attribute__((visibility("default"))) int kvq_debug_kernel_events(vo
   g_ev_stop = static_cast<cudaEvent_t>(stop_event);
   return KVQ_OK;
 }
+
+// ------------------------------------------------------------------------------------------------------
+// Attention without a caller-provided workspace.
+//
+// Some callers may not allocate device memory at all: a serving engine that has already handed every free
+// byte to its KV-cache pool, a plugin running inside another framework's memory pool or while that framework
+// captures a CUDA graph, a real-time loop where cudaMalloc's implicit synchronization is unacceptable. For
+// them the scratch of the attention kernels (work plan, split-KV partials, status word) lives in a fixed
+// array in the library's own device image. Every GPU that loads the library holds these KVQ_STATIC_WS_BYTES
+// until the process exits.
+// ------------------------------------------------------------------------------------------------------
+namespace kvq {
+namespace {
+
+constexpr size_t KVQ_STATIC_WS_BYTES = 10u << 20;  // 10 MiB: enough for 592 CTAs (148 SMs x 4) and ~150k requests
+static __device__ __align__(256) unsigned char g_static_ws[KVQ_STATIC_WS_BYTES];
+
+// Device address of g_static_ws per device. In host code the symbol g_static_ws is only a stand-in: it must go
+// through cudaGetSymbolAddress (with the device current) before a kernel can use it.
+void* g_static_ws_ptr[64] = {};
+
+int static_workspace(void** out) {
+  int dev = 0;
+  KVQ_CUDA(cudaGetDevice(&dev));
+  KVQ_REQUIRE(dev >= 0 && dev < 64, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g_static_ws_ptr[dev]) {
+    void* p = nullptr;
+    KVQ_CUDA(cudaGetSymbolAddress(&p, g_static_ws));
+    g_static_ws_ptr[dev] = p;
+  }
+  *out = g_static_ws_ptr[dev];
+  return KVQ_OK;
+}
+
+}  // namespace
+}  // namespace kvq
+
+extern "C" __attribute__((visibility("default"))) size_t kvq_static_workspace_bytes(void) { return KVQ_STATIC_WS_BYTES; }
+
+extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_noalloc(
+    const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q, const int32_t* seq_lens,
+    const int32_t* block_table, const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+    int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks, int64_t q_stride_t,
+    int64_t q_stride_h, int64_t o_stride_t, int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n,
+    int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+    int k_per_channel, int v_per_channel, int max_query_len, int qmax, kvq_stream_t stream) {
+  if (num_seqs > 0 && (head_dim == 64 || head_dim == 128)) {
+    const size_t need = kvq_decode_workspace_size(num_seqs, head_dim);
+    if (need == 0) return KVQ_ERR_CUDA;  // message already set
+    if (need > KVQ_STATIC_WS_BYTES) {
+      set_error("kvq_int8_decode_attention_noalloc: %d requests need %zu bytes of scratch, the built-in array holds %zu; "
+                "use kvq_int8_decode_attention with a caller-provided workspace",
+                num_seqs, need, static_cast<size_t>(KVQ_STATIC_WS_BYTES));
+      return KVQ_ERR_WORKSPACE;
+    }
+  }
+  void* ws = nullptr;
+  const int rc = static_workspace(&ws);
+  if (rc != KVQ_OK) return rc;
+  return kvq_int8_decode_attention(q, k_cache, v_cache, out, cu_q, seq_lens, block_table, k_scale, v_scale, softmax_scale,
+                                   num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, q_stride_t,
+                                   q_stride_h, o_stride_t, o_stride_h, kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b,
+                                   vc_stride_n, vc_stride_h, bt_stride, k_per_channel, v_per_channel, max_query_len, qmax,
+                                   ws, KVQ_STATIC_WS_BYTES, stream);
+}

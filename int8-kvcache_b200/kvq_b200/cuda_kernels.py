@@ -264,7 +264,7 @@ def check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan):
     """KVQ_DEBUG=1: host-side bounds checks of one batch before the kernels run; raises
     RuntimeError("kvq input check: ...") like the reference (kvq/cuda_kernels.py:134-169). Synchronizes, so it
     is skipped while a CUDA graph is being captured."""
-    if torch.cuda.is_current_stream_capturing():
+    if q.is_cuda and torch.cuda.is_current_stream_capturing():
         return
     starts = cu_seqlens_q.cpu().numpy().astype(np.int64)
     ctx = seq_lens.cpu().numpy().astype(np.int64)

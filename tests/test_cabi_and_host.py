@@ -1,0 +1,156 @@
+"""CPU tests: the C-ABI library loads and exports what include/kvq_b200.h declares (no compute calls), and the host
+logic of the package (page plan, scale files and their TP sharding, input checks, loud failure without the native
+library, vLLM surface)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+from conftest import ROOT, load_golden
+
+from kvq_b200 import _native, scales
+from kvq_b200 import cuda_kernels as ck
+
+HEADER = os.path.join(ROOT, "include", "kvq_b200.h")
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", open(HEADER).read(), flags=re.S)
+    out = {}
+    for m in re.finditer(r"\b(?:int|size_t|const char\*)\s+(kvq_\w+)\s*\(([^;]*?)\)\s*;", text, flags=re.S):
+        params = m.group(2).strip()
+        out[m.group(1)] = 0 if params == "void" else len([p for p in params.split(",") if p.strip()])
+    return out
+
+
+def test_library_exports_every_declared_symbol():
+    decl = declared_functions()
+    assert len(decl) >= 10 and "kvq_int8_decode_attention" in decl and "kvq_quant_cache" in decl
+    handle = ctypes.CDLL(_native.LIB_PATH)
+    for name in decl:
+        assert hasattr(handle, name), f"{name} declared in kvq_b200.h but not exported"
+    lib = _native.lib()
+    assert lib.kvq_version() >= 100 and lib.kvq_last_error() == b""
+
+
+def test_ctypes_signatures_match_header():
+    decl = declared_functions()
+    assert set(decl) == set(_native.SIGNATURES), set(decl) ^ set(_native.SIGNATURES)
+    for name, nparams in decl.items():
+        assert len(_native.SIGNATURES[name][1]) == nparams, name
+
+
+def test_argument_errors_are_reported_without_a_gpu():
+    """Validation happens before any CUDA call: bad head_dim -> KVQ_ERR_INVALID_ARGUMENT + message."""
+    lib = _native.lib()
+    rc = lib.kvq_quant_q(None, None, None, None, 4, 28, 4, 96, 128, 0, 0, 1, None)
+    assert rc == 1 and b"head_dim 128" in lib.kvq_last_error()
+    with pytest.raises(RuntimeError, match="kvq_b200"):
+        _native.check(rc)
+    assert lib.kvq_quant_cache(*([None] * 8), 0, 4, 128, 16, *([0] * 10), 1, 1, None) == 0   # empty batch: silent
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(_native, "_LIB", None)
+    monkeypatch.setattr(_native, "LIB_PATH", "/nonexistent/libkvq_b200.so")
+    with pytest.raises(RuntimeError, match="no non-CUDA fallback"):
+        _native.lib()
+
+
+def test_cpu_tensors_are_rejected():
+    case_q = torch.zeros(2, 28, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ck.quant_q(case_q, torch.ones(4, 128))
+
+
+def test_plan_long_matches_reference_tables():
+    fx = load_golden("plan_long.npz")
+    for key in ("a", "b", "c", "none"):
+        plan = ck.plan_long(fx[f"{key}_cu"], fx[f"{key}_sl"], int(fx[f"{key}_bs"]))
+        if bool(fx[f"{key}_is_none"]):
+            assert plan is None
+            continue
+        assert np.array_equal(plan.src_req, fx[f"{key}_src_req"]) and plan.src_req.dtype == np.int32
+        assert np.array_equal(plan.src_j, fx[f"{key}_src_j"]) and np.array_equal(plan.block_table, fx[f"{key}_bt"])
+        assert plan.max_seqlen_k == int(fx[f"{key}_max_seqlen_k"]) and plan.has_short == bool(fx[f"{key}_has_short"])
+    # the reference's literal known answers (tests/test_cuda_kernels.py:88-97 there)
+    plan = ck.plan_long(torch.tensor([0, 1, 13, 14, 314], dtype=torch.int32), torch.tensor([50, 40, 9, 330]), 16)
+    assert plan.src_req.tolist() == [1] * 3 + [3] * 21 and plan.src_j.tolist() == list(range(3)) + list(range(21))
+    assert plan.block_table.shape[1] * 16 >= 330 + 256 and not plan.block_table[3, 21:].any()
+    assert ck.plan_long(torch.tensor([0, 1, 9]), torch.tensor([5, 8]), 16) is None   # q_len 8 is still short
+
+
+def test_scale_sharding_matches_reference():
+    fx = load_golden("scale_shards.npz")
+    for name in ("t8", "t2"):
+        t = torch.from_numpy(fx[name])
+        for tp in (1, 2, 4, 8):
+            for rank in range(tp):
+                assert np.array_equal(scales.shard(t, rank, tp).numpy(), fx[f"{name}_tp{tp}_r{rank}"])
+    with pytest.raises(ValueError):
+        scales.shard(torch.zeros(6, 4), 0, 4)
+
+
+def test_scale_file_round_trip(tmp_path):
+    g = torch.Generator().manual_seed(0)
+    layers = {f"model.layers.{i}.self_attn.attn": {"k_scale": torch.rand(4, 128, generator=g), "v_scale": torch.rand(4, 128, generator=g),
+                                                   "k_mu": torch.randn(4, 128, generator=g)} for i in range(3)}
+    path = str(tmp_path / "scales.safetensors")
+    scales.save(path, layers)
+    back = scales.load(path)
+    assert set(back) == set(layers)
+    for name, fields in layers.items():
+        for f, t in fields.items():
+            assert back[name][f].dtype == torch.float32 and torch.equal(back[name][f], t)
+    mine = scales.for_layer(back, "model.layers.1.self_attn.attn", 1, 2, "cpu")
+    assert torch.equal(mine["k_scale"], layers["model.layers.1.self_attn.attn"]["k_scale"][2:4])
+    # key format of the file: "<layer>|<field>"
+    from safetensors.torch import load_file
+    assert "model.layers.0.self_attn.attn|k_mu" in load_file(path)
+
+
+def test_from_stats_and_merge_tp():
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(500, 4, 16, generator=g) * 3 + 1
+    st = {"tokens": 500, "k_sum": x.sum(0), "k_max": x.amax(0), "k_min": x.amin(0), "k_absmax": x.abs().amax(0),
+          "v_absmax": x.abs().amax(0)}
+    s = scales.from_stats(st, smooth_k=True)
+    mu = x.mean(0)
+    assert torch.allclose(s["k_mu"], mu, atol=1e-5)
+    assert torch.allclose(s["k_scale"], ((x - mu).abs().amax(0) / 127).clamp(min=1e-8), rtol=1e-5)
+    assert scales.from_stats(st, granularity="per_head")["v_scale"].shape == (4, 1)
+    halves = [{"tp_rank": r, "stats": {"l": {k: (v if k == "tokens" else v[2 * r:2 * r + 2]) for k, v in st.items()}},
+               "samples": {"l": {"k": x[:, 2 * r:2 * r + 2], "v": x[:, 2 * r:2 * r + 2]}}} for r in (1, 0)]
+    stats, samples = scales.merge_tp(halves, 4)
+    assert torch.equal(stats["l"]["k_absmax"], st["k_absmax"]) and torch.equal(samples["l"]["k"], x)
+
+
+def test_check_inputs_messages():
+    c = {"q": torch.zeros(3, 28, 128), "k": torch.zeros(8, 16, 4, 128, dtype=torch.int8)}
+    cu = torch.tensor([0, 1, 3], dtype=torch.int32)
+    ok_bt = torch.tensor([[0, 1, 2], [3, 4, 5]], dtype=torch.int32)
+    ck.check_inputs(c["q"], c["k"], cu, torch.tensor([40, 20], dtype=torch.int32), ok_bt, None)
+    with pytest.raises(RuntimeError, match="kvq input check: .*outside"):
+        ck.check_inputs(c["q"], c["k"], cu, torch.tensor([40, 20], dtype=torch.int32), ok_bt + 6, None)
+    with pytest.raises(RuntimeError, match="seq_len 1 < q_len 2"):
+        ck.check_inputs(c["q"], c["k"], cu, torch.tensor([40, 1], dtype=torch.int32), ok_bt, None)
+    with pytest.raises(RuntimeError, match="pages > block_table width"):
+        ck.check_inputs(c["q"], c["k"], cu, torch.tensor([400, 20], dtype=torch.int32), ok_bt, None)
+
+
+def test_vllm_surface():
+    pytest.importorskip("vllm")
+    from kvq_b200 import vllm_plugin
+    from kvq_b200.vllm_int8 import backend as b
+
+    assert b.Int8StaticBackend.get_name() == "CUSTOM" and b.Int8StaticBackend.supported_kv_cache_dtypes == ["int8_static"]
+    assert b.Int8StaticBackend.get_impl_cls() is b.Int8StaticImpl and b.Int8StaticBackend.get_builder_cls() is b.Int8StaticBuilder
+    assert vllm_plugin.BACKEND_PATH.endswith("Int8StaticBackend")
+    kv = torch.arange(2 * 2 * 16 * 4 * 8, dtype=torch.int32).to(torch.int8).reshape(2, 2, 16, 4, 8)
+    k, v = b.split_kv_cache(kv, 8)
+    assert k.shape == (2, 16, 4, 8) and torch.equal(k, kv[:, 0]) and torch.equal(v, kv[:, 1])
+    kv32 = torch.zeros(2, 16, 4, 16, dtype=torch.int8).transpose(1, 2)     # logical [nb, H, block, 2D]
+    k, v = b.split_kv_cache(kv32, 8)
+    assert k.shape == (2, 16, 4, 8) and k.stride() == (1024, 64, 16, 1) and v.storage_offset() == 8

@@ -287,6 +287,87 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------------------------------------
+# --suite kernels: every kernel of the path on the other benchmark configurations (one JSON line each)
+# --------------------------------------------------------------------------------------------------------
+def run_suite(args):
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    from kvq_b200 import cuda_kernels as ck
+    from kvq_b200 import workloads
+
+    peak, _ = peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # 2x L2: written before every timed call
+
+    def timed(fn, reps=20):
+        """Median device time of one call, replayed from a CUDA graph (so host launch overhead of the Python
+        wrapper does not sit between the events), L2 flushed before every replay."""
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return float(np.median(ts))
+
+    def emit(kernel, workload, us, nbytes, **extra):
+        print(json.dumps({"suite": "kernels", "kernel": kernel, "workload": workload, "us": round(us, 2),
+                          "algorithmic_bytes": nbytes, "GBps": round(nbytes / us / 1e3, 1),
+                          "frac_of_measured_peak": round(nbytes / us / 1e3 / peak, 3), "l2": "flushed between calls", "timing": "CUDA-graph replay between events, median of 20",
+                          **extra}), flush=True)
+
+    # fused quantize + cache write (config 1 = 8192 tokens) and the page dequantization of what was written
+    for T in (64, 256, 2048, 8192):
+        c = workloads.write_case(1001, T, HKV, D, num_blocks=4096, block_size=BLOCK, smooth=False)
+        st = {k: v.to(dev) for k, v in c["static"].items()}
+        key, value, slots = c["key"].to(dev), c["value"].to(dev), c["slots"].to(dev)
+        kc = torch.zeros(4096, BLOCK, HKV, D, dtype=torch.int8, device=dev)
+        vc = torch.zeros_like(kc)
+        us = timed(lambda: ck.quant_reshape_and_cache(key, value, kc, vc, slots, st))
+        emit("quant_cache_kernel", f"{T} tokens x {HKV} x {D} K and V into a 65536-slot cache", us, T * (HKV * D * 6 + 8))
+    for P in (512, 8192):
+        kc = torch.randint(-127, 128, (P, BLOCK, HKV, D), dtype=torch.int8, device=dev)
+        vc = torch.randint(-127, 128, (P, BLOCK, HKV, D), dtype=torch.int8, device=dev)
+        ko = torch.empty(P, BLOCK, HKV, D, dtype=torch.bfloat16, device=dev)
+        vo = torch.empty_like(ko)
+        ids = torch.randperm(P, device=dev).to(torch.int32)
+        zero, idx = torch.zeros(P, dtype=torch.int32, device=dev), torch.arange(P, dtype=torch.int32, device=dev)
+        us = timed(lambda: ck.dequant_pages(kc, vc, ko, vo, ids[None].contiguous(), zero, idx, st))
+        emit("dequant_pages_kernel", f"{P} pages x {BLOCK} x {HKV} x {D}, K and V", us, P * BLOCK * HKV * D * 2 * 3)
+    for T in (128, 2048):
+        q = torch.randn(T, HQ, D, device=dev).to(torch.bfloat16)
+        us = timed(lambda: ck.quant_q(q, st["k_scale"]))
+        emit("quant_q_kernel<128>", f"{T} tokens x {HQ} heads", us, T * HQ * D * 3 + T * HQ * 4,
+             note="includes the two output allocations of the reference-compatible wrapper")
+    # decode attention over batch x context (whole call: plan + decode + merge)
+    for batch, ctx in ((1, 32768), (8, 32768), (32, 32768), (64, 4096), (128, 4096), (256, 1024)):
+        c = workloads.decode_batch_on_device(batch, ctx, dev, seed=5)
+        out = torch.empty_like(c["q"])
+        us = timed(lambda: ck.decode_attention(c["q"], c["kq"], c["vq"], out, c["cu_seqlens_q"], c["seq_lens"],
+                                               c["block_table"], c["softmax_scale"], c["static"]))
+        emit("decode_attention (3 launches)", f"{batch} x {ctx}, q_len 1", us, kv_bytes(c["seq_lens_list"]))
+        del c
+    # config 3: 256 requests, q_len 8, contexts uniform in [1024, 8192]
+    c = workloads.decode_batch_on_device(256, 0, dev, seed=1003, q_len=8, ctx_range=(1024, 8192))
+    out = torch.empty_like(c["q"])
+    us = timed(lambda: ck.decode_attention(c["q"], c["kq"], c["vq"], out, c["cu_seqlens_q"], c["seq_lens"],
+                                           c["block_table"], c["softmax_scale"], c["static"], max_query_len=8))
+    emit("decode_attention (3 launches)", "config 3: 256 requests, q_len 8, ctx U[1024, 8192]", us,
+         kv_bytes(c["seq_lens_list"]), note="KV bytes counted once although 4 m tiles (56 rows) read them")
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu capture summarised in
 # profiles/decode_kernel_16x32k_ncu_full.md: 541,869,312 bytes for 16 requests x 32768 context. Traffic is
 # proportional to the requests (every CTA streams its slice of the KV bytes once), so it is scaled to the batch.
@@ -302,6 +383,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU (default: the headline 128)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (default: the headline 32768)")
+    ap.add_argument("--suite", default=None, choices=["kernels"], help="extra per-kernel lines instead of the headline")
     ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
@@ -314,6 +396,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU (there is no CPU path for the product arm)")
+    if args.suite == "kernels":
+        run_suite(args)
+        return
     run_ours(args, rank, world, local_rank)
 
 

@@ -566,32 +566,79 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 // ------------------------------------------------------------------------------------------------------
 // merge of items that were cut across CTAs
 // ------------------------------------------------------------------------------------------------------
+constexpr int MERGE_THREADS = 256;
+
+// One block per (CTA boundary, row). Boundary b is the unit b * W where decode CTA b - 1 stops and CTA b starts;
+// the item that contains it strictly inside was cut there. An item cut by several boundaries is merged by the
+// first of them. The grid therefore depends only on the decode grid, not on the batch. The partials of the
+// item are spread over threads: D / 4 lanes read one partial's row as float4, MERGE_THREADS / (D / 4) partials
+// are in flight per step, so an item cut over hundreds of CTAs (one long request on an otherwise idle GPU)
+// merges in a few dependent load rounds.
 template <int D>
-__global__ void __launch_bounds__(D) merge_kernel(const DecodeArgs a, int mtiles_max) {
-  const int req = blockIdx.x, kvh = blockIdx.y / mtiles_max, mt = blockIdx.y - kvh * mtiles_max;
+__global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a) {
+  constexpr int LPP = D / 4, PG = MERGE_THREADS / LPP;   // lanes per partial, partials per step
+  __shared__ float s_red[MERGE_THREADS / 32];
+  __shared__ float4 s_num[PG][LPP];
+  __shared__ float s_den[PG];
+  __shared__ int s_req;
+  const int row = blockIdx.y, tid = threadIdx.x;
+  const int total = a.hdr[1], W = a.hdr[2];
+  const int64_t u64 = static_cast<int64_t>(blockIdx.x + 1) * W;
+  if (u64 >= total) return;
+  const int u = static_cast<int>(u64);
+  for (int r = tid; r < a.num_seqs; r += MERGE_THREADS)
+    if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
+  __syncthreads();
+  const int req = s_req;
   const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok;
   int nchunks, mtiles;
-  if (units_of(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, nchunks, mtiles) == 0 || mt >= mtiles) return;
-  const int W = a.hdr[2];
-  const int A = a.prefix[req] + (kvh * mtiles + mt) * nchunks, B = A + nchunks;
+  units_of(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, nchunks, mtiles);
+  const int p0 = a.prefix[req];
+  const int item = (u - p0) / nchunks, kvh = item / mtiles, mt = item - kvh * mtiles;
+  const int A = p0 + item * nchunks, B = A + nchunks;
   const int c_lo = A / W, c_hi = (B - 1) / W;
-  if (c_lo == c_hi) return;  // the item was finished by one CTA
-  const int d = threadIdx.x;
-  for (int row = 0; row < PART_ROWS; ++row) {
-    const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-    if (rt >= qlen) break;
-    // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
-    auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * PART_ROWS + row; };
-    float M = -1e30f;
-    for (int c = c_lo; c <= c_hi; ++c) M = fmaxf(M, a.part_ml[slot_of(c) * 2]);
-    float num = 0.f, den = 0.f;
-    for (int c = c_lo; c <= c_hi; ++c) {
-      const int s = slot_of(c);
-      const float w = ex2((a.part_ml[s * 2] - M) * LOG2E);
-      den += w * a.part_ml[s * 2 + 1];
-      num += w * a.part_acc[static_cast<int64_t>(s) * D + d];
+  if (A == u || c_lo != static_cast<int>(blockIdx.x)) return;  // not cut here, or an earlier boundary merges it
+  const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+  if (rt >= qlen) return;
+  // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
+  auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * PART_ROWS + row; };
+  const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
+
+  float M = -1e30f;
+  for (int i = tid; i < np; i += MERGE_THREADS) M = fmaxf(M, a.part_ml[slot_of(c_lo + i) * 2]);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+  if (lane == 0) s_red[warp] = M;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
+
+  const int pg = tid / LPP, l4 = tid - pg * LPP;
+  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+  float den = 0.f;
+#pragma unroll 4
+  for (int i = pg; i < np; i += PG) {
+    const int sl = slot_of(c_lo + i);
+    const float w = ex2((a.part_ml[sl * 2] - M) * LOG2E);
+    const float4 x = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(sl) * D + l4 * 4);
+    num.x += w * x.x, num.y += w * x.y, num.z += w * x.z, num.w += w * x.w;
+    den += w * a.part_ml[sl * 2 + 1];
+  }
+  s_num[pg][l4] = num;
+  if (l4 == 0) s_den[pg] = den;
+  __syncthreads();
+  if (tid < LPP) {
+    float4 t = s_num[0][tid];
+    float dsum = s_den[0];
+#pragma unroll
+    for (int g = 1; g < PG; ++g) {   // fixed order: the result does not depend on scheduling
+      const float4 x = s_num[g][tid];
+      t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
+      dsum += s_den[g];
     }
-    a.out[(tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + d] = __float2bfloat16_rn(num / fmaxf(den, 1e-30f));
+    const float inv = 1.f / fmaxf(dsum, 1e-30f);
+    *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + tid * 4) =
+        make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
   }
 }
 
@@ -775,7 +822,6 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
 
   const int G = num_q_heads / num_kv_heads;
   const int max_q = std::max(1, std::min(max_query_len, qmax));
-  const int mtiles_max = (G * max_q + 15) / 16;
   const bool rows16 = G * max_q > 8;
   const int occ = di->occ[head_dim == 128][rows16];
   const int grid = di->sms * occ;
@@ -818,14 +864,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     else
       decode_kernel<128, false><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    merge_kernel<128><<<dim3(num_seqs, num_kv_heads * mtiles_max), 128, 0, s>>>(a, mtiles_max);
+    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
   } else {
     if (rows16)
       decode_kernel<64, true><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
     else
       decode_kernel<64, false><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    merge_kernel<64><<<dim3(num_seqs, num_kv_heads * mtiles_max), 64, 0, s>>>(a, mtiles_max);
+    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;

@@ -45,17 +45,11 @@ __global__ void __launch_bounds__(kThreads) quant_cache_kernel(const QuantCacheA
   const int64_t tok = i / per_tok;
   const int rem = static_cast<int>(i - tok * per_tok);
   const int h = rem / a.groups, d0 = (rem - h * a.groups) * 16;
-  const int64_t slot = __ldg(a.slots + tok);
-  if (slot < 0) return;  // padding token
-  int64_t blk, off;
-  if (a.bs_shift >= 0) {
-    blk = slot >> a.bs_shift, off = slot & (a.block_size - 1);
-  } else {
-    blk = slot / a.block_size, off = slot - blk * a.block_size;
-  }
+  // every load below is independent of the slot: issue them all before looking at it (one DRAM round trip)
   float k[16], v[16], sk[16], sv[16], mu[16];
   load16bf(a.key + tok * a.k_st + h * a.k_sh + d0, k);
   load16bf(a.value + tok * a.v_st + h * a.v_sh + d0, v);
+  const int64_t slot = __ldg(a.slots + tok);
   load16f(a.kmu + h * a.D + d0, mu);
   if (a.pc_k) {
     load16f(a.ks + h * a.D + d0, sk);
@@ -70,6 +64,13 @@ __global__ void __launch_bounds__(kThreads) quant_cache_kernel(const QuantCacheA
     const float s = __ldg(a.vs + h);
 #pragma unroll
     for (int e = 0; e < 16; ++e) sv[e] = s;
+  }
+  if (slot < 0) return;  // padding token
+  int64_t blk, off;
+  if (a.bs_shift >= 0) {
+    blk = slot >> a.bs_shift, off = slot & (a.block_size - 1);
+  } else {
+    blk = slot / a.block_size, off = slot - blk * a.block_size;
   }
   uint32_t kw[4], vw[4];
 #pragma unroll
@@ -126,7 +127,7 @@ __global__ void __launch_bounds__(kThreads) quant_q_kernel(const __nv_bfloat16* 
 
 // ------------------------------------------------------------------------------------------------------
 // Page dequantization. Item = (output page, slot, kv head, 16-channel group); the output is contiguous
-// [pages, block, H, D], so item i writes 32 bytes at element offset 16 * i of each output.
+// [pages, block, H, D], so item i of page p writes 32 bytes at element offset 16 * (p * items_per_page + i).
 // ------------------------------------------------------------------------------------------------------
 struct DequantArgs {
   const int8_t *kc, *vc;
@@ -139,8 +140,7 @@ struct DequantArgs {
   int pc_k, pc_v;
 };
 
-__device__ __forceinline__ void dequant16(const int8_t* src, __nv_bfloat16* dst, const float* scale, int per_channel) {
-  const uint4 raw = ld_stream16(src);
+__device__ __forceinline__ void dequant_store(uint4 raw, __nv_bfloat16* dst, const float* scale, int per_channel) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
   float s[16];
   if (per_channel) {
@@ -165,19 +165,38 @@ __device__ __forceinline__ void dequant16(const int8_t* src, __nv_bfloat16* dst,
   reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// One CTA per output page: the source page id is looked up once, then every thread issues all of its 16-byte
+// loads (kUnroll items of K and of V) before converting any of them.
+constexpr int kUnroll = 2;
+
 __global__ void __launch_bounds__(kThreads) dequant_pages_kernel(const DequantArgs a) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (i >= a.n_items) return;
+  const int64_t p = blockIdx.x;
   const int per_slot = a.H * a.groups, per_page = a.block_size * per_slot;
-  const int64_t p = i / per_page;
-  const int rem = static_cast<int>(i - p * per_page);
-  const int n = rem / per_slot, rem2 = rem - n * per_slot;
-  const int h = rem2 / a.groups, d0 = (rem2 - h * a.groups) * 16;
   const int64_t src = __ldg(a.block_table + static_cast<int64_t>(__ldg(a.src_req + p)) * a.bt_stride + __ldg(a.src_j + p));
-  dequant16(a.kc + src * a.kc_sb + n * a.kc_sn + h * a.kc_sh + d0, a.ko + i * 16,
-            a.pc_k ? a.ks + h * a.D + d0 : a.ks + h, a.pc_k);
-  dequant16(a.vc + src * a.vc_sb + n * a.vc_sn + h * a.vc_sh + d0, a.vo + i * 16,
-            a.pc_v ? a.vs + h * a.D + d0 : a.vs + h, a.pc_v);
+  const int8_t* kp = a.kc + src * a.kc_sb;
+  const int8_t* vp = a.vc + src * a.vc_sb;
+  for (int base = threadIdx.x; base < per_page; base += kThreads * kUnroll) {
+    uint4 kr[kUnroll], vr[kUnroll];
+    int hh[kUnroll], dd[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      const int n = i / per_slot, rem = i - n * per_slot;
+      hh[u] = rem / a.groups, dd[u] = (rem - hh[u] * a.groups) * 16;
+      if (i < per_page) {
+        kr[u] = ld_stream16(kp + n * a.kc_sn + hh[u] * a.kc_sh + dd[u]);
+        vr[u] = ld_stream16(vp + n * a.vc_sn + hh[u] * a.vc_sh + dd[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int i = base + u * kThreads;
+      if (i >= per_page) continue;
+      const int64_t o = (p * per_page + i) * 16;
+      dequant_store(kr[u], a.ko + o, a.pc_k ? a.ks + hh[u] * a.D + dd[u] : a.ks + hh[u], a.pc_k);
+      dequant_store(vr[u], a.vo + o, a.pc_v ? a.vs + hh[u] * a.D + dd[u] : a.vs + hh[u], a.pc_v);
+    }
+  }
 }
 
 int ilog2_exact(int x) {
@@ -278,8 +297,7 @@ extern "C" __attribute__((visibility("default"))) int kvq_dequant_pages(const vo
   a.kc_sb = kc_stride_b, a.kc_sn = kc_stride_n, a.kc_sh = kc_stride_h;
   a.vc_sb = vc_stride_b, a.vc_sn = vc_stride_n, a.vc_sh = vc_stride_h;
   a.pc_k = k_per_channel, a.pc_v = v_per_channel;
-  const int64_t blocks = (a.n_items + kThreads - 1) / kThreads;
-  dequant_pages_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  dequant_pages_kernel<<<static_cast<unsigned>(num_pages), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
 }

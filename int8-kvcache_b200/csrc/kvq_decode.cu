@@ -44,7 +44,7 @@ struct DecodeArgs {
   const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units
   float* part_acc;         // [grid * 2][16][D]  numerator * v_scale of a cut item
   float* part_ml;          // [grid * 2][16][2]  running max of the scores, denominator
-  double sm_scale;       // softmax scale, natural-log domain
+  float sm_hi, sm_lo;      // softmax scale (natural-log domain) as an unevaluated fp32 pair
   int num_seqs, Hq, Hkv, G, lbs, bs_mask, qmax;
   int64_t q_st, q_sh, o_st, o_sh, bt_stride;
   int pc_k, pc_v;
@@ -117,6 +117,34 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 constexpr float LOG2E = 1.4426950408889634f;
+
+#ifdef KVQ_TIMELINE   // debug builds only: per-CTA cycle stamps of the first item, read back by a probe
+__device__ long long g_timeline[1024 * 16];
+#define KVQ_TL(i) do { if (threadIdx.x == 0 && first_seg) g_timeline[blockIdx.x * 16 + (i)] = clock64(); } while (0)
+#else
+#define KVQ_TL(i) do { } while (0)
+#endif
+
+// Unevaluated sum hi + lo of two floats (|lo| <= ulp(hi) / 2): ~48 bits of significand without FP64 instructions.
+struct ff {
+  float hi, lo;
+};
+__device__ __forceinline__ ff fast_two_sum(float a, float b) {  // |a| >= |b|
+  const float s = __fadd_rn(a, b);
+  return ff{s, __fadd_rn(b, -__fadd_rn(s, -a))};
+}
+__device__ __forceinline__ ff two_prod(float a, float b) {
+  const float p = __fmul_rn(a, b);
+  return ff{p, __fmaf_rn(a, b, -p)};
+}
+__device__ __forceinline__ ff ff_mul(ff a, ff b) {
+  const float p = __fmul_rn(a.hi, b.hi);
+  float e = __fmaf_rn(a.hi, b.hi, -p);
+  e = __fmaf_rn(a.hi, b.lo, e);
+  e = __fmaf_rn(a.lo, b.hi, e);
+  return fast_two_sum(p, e);
+}
+__device__ __forceinline__ ff ff_max(ff a, ff b) { return (b.hi > a.hi || (b.hi == a.hi && b.lo > a.lo)) ? b : a; }
 
 // fp32(dot * c) for c = hi + lo: the product is formed to ~48 bits and rounded once, like the reference's
 // float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100 that moves
@@ -246,12 +274,14 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 
   int u = ubeg;
   bool first_seg = true;
+  KVQ_TL(0);
   while (u < uend) {
     // ---- find the request that owns unit u: prefix[r] <= u < prefix[r + 1] ----
     for (int r = tid; r < a.num_seqs; r += NTHREADS)
       if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
     __syncthreads();
     const int req = s_req;
+    KVQ_TL(1);
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
     int nchunks, mtiles;
     units_of(qlen, L, a.G, a.Hkv, a.qmax, nchunks, mtiles);
@@ -306,17 +336,26 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       int issued = 0;
       if (ok)
         for (; issued < min(nw, NSTAGE - 1); ++issued) issue(issued);
+      KVQ_TL(2);
 
-      // -- q prologue: fold s_k, quantize per row; 8 threads per row. Done in double like the reference's
-      //    implementation B (exact products, double scale and division); it runs once per item. --
+      // -- q prologue: fold s_k, quantize per row; 8 threads per row. The reference's implementation B does this
+      //    in double (exact products q * s_k, scale = max / 127, division). FP64 issue is slow enough on this part
+      //    to cost microseconds per item, so the same values are carried as unevaluated fp32 pairs (~2^-46). --
       {
         constexpr int CPT = D / 8;
         const int row = tid >> 3, part = tid & 7, d0 = part * CPT;
         const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
         float x[CPT];   // fp32(q * s_k): what gets quantized
-        double amax = 0.0;
+        ff amax = {0.f, 0.f};
 #pragma unroll
         for (int e = 0; e < CPT; ++e) x[e] = 0.f;
+        float sk[CPT];   // vector loads issued up front: scalar loads inside the loop would serialize on L2 latency
+#pragma unroll
+        for (int v4 = 0; v4 < CPT / 4; ++v4) {
+          const float4 t4 = a.pc_k ? __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0) + v4)
+                                   : make_float4(1.f, 1.f, 1.f, 1.f);
+          sk[4 * v4] = t4.x, sk[4 * v4 + 1] = t4.y, sk[4 * v4 + 2] = t4.z, sk[4 * v4 + 3] = t4.w;
+        }
         if (rt < qlen) {
           const __nv_bfloat16* qp = a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0;
 #pragma unroll
@@ -328,22 +367,42 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           }
 #pragma unroll
           for (int e = 0; e < CPT; ++e) {
-            const double xd = a.pc_k ? static_cast<double>(x[e]) * static_cast<double>(__ldg(a.ks + kvh * D + d0 + e))
-                                     : static_cast<double>(x[e]);
-            amax = fmax(amax, fabs(xd));
-            x[e] = static_cast<float>(xd);
+            const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo (sk = 1 for a per-head K scale)
+            x[e] = p.hi;
+            amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
           }
         }
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) amax = fmax(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-        const double sq = fmax(amax / 127.0, 1e-8);
+        for (int o = 1; o < 8; o <<= 1)
+          amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
+        // sq = max(amax / 127, 1e-8)
+        ff sq;
+        {
+          const float q1 = __fdiv_rn(amax.hi, 127.f);
+          const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
+          sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
+          constexpr float E_HI = 1e-8f;
+          const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
+          if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
+        }
         uint32_t w[CPT / 4];
 #pragma unroll
         for (int k = 0; k < CPT / 4; ++k) {
           int b[4];
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            b[e] = max(-127, min(127, __double2int_rn(static_cast<double>(x[4 * k + e]) / sq)));
+          for (int e = 0; e < 4; ++e) {
+            // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
+            // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
+            // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
+            const float xe = x[4 * k + e];
+            const float qf = __fdiv_rn(xe, sq.hi);
+            int r = __float2int_rn(qf);
+            if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-3f) {
+              const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
+              r = __double2int_rn(static_cast<double>(xe) / sqd);
+            }
+            b[e] = max(-127, min(127, r));
+          }
           w[k] = pack4(b[0], b[1], b[2], b[3]);
         }
         if constexpr (CPT == 16)
@@ -352,10 +411,11 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           *reinterpret_cast<uint2*>(&s_q[row * QROW + d0]) = make_uint2(w[0], w[1]);
         if (part == 0) {
           // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
-          const double c = sq * (a.pc_k ? 1.0 : static_cast<double>(__ldg(a.ks + kvh))) * a.sm_scale;
-          const float hi = static_cast<float>(c);
-          s_chi[row] = hi;
-          s_clo[row] = static_cast<float>(c - static_cast<double>(hi));
+          ff c = sq;
+          if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
+          c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
+          s_chi[row] = c.hi;
+          s_clo[row] = c.lo;
         }
       }
       __syncthreads();
@@ -375,6 +435,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       };
       const int lim0 = row_lim(g), lim1 = row_lim(g + 8);
       const int lim_all = L - qlen + 1;  // every row sees keys below this
+      KVQ_TL(3);
 
       float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
       float acc[NT][ROWS16 ? 4 : 2];
@@ -389,6 +450,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         const uint32_t gi = gbase + i, st = gi % NSTAGE;
         ok = __all_sync(0xffffffffu, mbar_wait(wbar + st * 8, (gi / NSTAGE) & 1));
         if (!ok) break;
+        if (i == 0) KVQ_TL(4);
         const uint32_t sk = wring + st * Gm::STAGE, sv = sk + Gm::TILE;
         const int n_base = (c0 + warp + NWARPS * i) * CHUNK;
 
@@ -488,6 +550,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         __syncwarp();  // every lane is done with this stage before lane 0 refills it
       }
       gbase += nw > 0 ? nw : 0;
+      KVQ_TL(5);
       if (!ok) atomicExch(a.hdr, 1);
 
       // -- combine the warps: weights exp2(m_w - M) --
@@ -522,6 +585,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       __syncthreads();
 
       // -- epilogue: 4 channels per thread and step; s_v applied here --
+      KVQ_TL(6);
       const int slot = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * PART_ROWS;
       for (int i = tid; i < NROWS * (D / 4); i += NTHREADS) {
         const int row = i / (D / 4), c4 = (i - row * (D / 4)) * 4;
@@ -558,6 +622,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       fence_proxy_async();
       __syncthreads();
       u += c1 - c0;
+      KVQ_TL(7);
       first_seg = false;
     }
   }
@@ -839,7 +904,8 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   a.prefix = reinterpret_cast<const int32_t*>(ws + wl.prefix);
   a.part_acc = reinterpret_cast<float*>(ws + wl.part_acc);
   a.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
-  a.sm_scale = softmax_scale;
+  a.sm_hi = static_cast<float>(softmax_scale);
+  a.sm_lo = static_cast<float>(softmax_scale - static_cast<double>(a.sm_hi));
   a.num_seqs = num_seqs, a.Hq = num_q_heads, a.Hkv = num_kv_heads, a.G = G, a.qmax = qmax;
   a.lbs = 0;
   while ((1 << a.lbs) < block_size) ++a.lbs;
@@ -948,3 +1014,10 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_
                                    vc_stride_n, vc_stride_h, bt_stride, k_per_channel, v_per_channel, max_query_len, qmax,
                                    ws, KVQ_STATIC_WS_BYTES, stream);
 }
+
+#ifdef KVQ_TIMELINE
+extern "C" __attribute__((visibility("default"))) int kvq_debug_timeline(long long* host, int n) {
+  KVQ_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * n));
+  return KVQ_OK;
+}
+#endif

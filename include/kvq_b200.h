@@ -115,9 +115,10 @@ int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream);
  * no cudaFree, no allocating library call): the scratch is a fixed array of kvq_static_workspace_bytes()
  * (10 MiB) inside the library's device image, resident on every GPU that loads the library until the process
  * exits. Inputs and outputs are still the caller's.
- *   - Limit: a batch whose scratch (kvq_decode_workspace_size) exceeds the array is rejected with
- *     KVQ_ERR_WORKSPACE and a message; nothing is launched. 10 MiB covers GPUs of up to 148 SMs and about
- *     150,000 requests per call.
+ *   - Limit: a batch whose minimal scratch exceeds the array is rejected with KVQ_ERR_WORKSPACE and a message;
+ *     nothing is launched. 10 MiB covers GPUs of up to 148 SMs and about 150,000 requests per call. Multi-token
+ *     queries run in the plain one-m-tile-per-item mode here (the grouped mode of kvq_int8_decode_attention needs
+ *     four times the partial area), which gives the same results but re-reads K/V once per m tile.
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
  *     current) and caches it; make that first call outside any stream capture.
  *   - All calls on a device share the one array, which keeps the previous call's contents. Nothing in it has

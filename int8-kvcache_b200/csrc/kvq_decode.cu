@@ -33,7 +33,8 @@ constexpr int NSTAGE = 3;      // TMA ring depth per warp
 constexpr int MIN_UNITS = 4;   // never give a CTA less than one chunk per warp
 constexpr int MAX_CTAS_PER_SM = 4;
 constexpr int HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total units, [2] units per CTA
-constexpr int PART_ROWS = 16;
+constexpr int PART_ROWS = 16;      // rows of one m tile
+constexpr int PART_ROWS_GROUPED = 64;  // rows of a group of up to four m tiles
 
 struct DecodeArgs {
   const __nv_bfloat16* q;
@@ -48,6 +49,8 @@ struct DecodeArgs {
   int num_seqs, Hq, Hkv, G, lbs, bs_mask, qmax;
   int64_t q_st, q_sh, o_st, o_sh, bt_stride;
   int pc_k, pc_v;
+  int grouped;             // 1: warps of a CTA share K/V streams across m tiles (multi-token queries)
+  int part_rows;           // rows per partial slot: 16, or 64 in grouped mode
   int kpos[3], vpos[3];    // tensor-map coordinate slot (1..3) of the (slot-in-block, head, block) dims
 };
 
@@ -61,6 +64,12 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -163,17 +172,27 @@ __device__ __forceinline__ uint32_t tile_off(int tau, int c16) {
   return off ^ (((off >> 7) & (D == 128 ? 7u : 3u)) << 4);
 }
 
-__device__ __forceinline__ int units_of(int qlen, int L, int G, int Hkv, int qmax, int& nchunks, int& mtiles) {
-  nchunks = max(1, (L + CHUNK - 1) / CHUNK);
-  mtiles = (qlen * G + 15) / 16;
-  return (qlen < 1 || qlen > qmax) ? 0 : nchunks * Hkv * mtiles;
+// Work of one request. A request with q_len query tokens has ceil(q_len * G / 16) m tiles of 16 (token, head) rows
+// per kv head. In grouped mode gs warps share one K/V stream and take one m tile each, so an item is a
+// (kv head, group of gs m tiles) pair; otherwise gs = 1 and every m tile is its own item. Units = 32-key chunks.
+struct ReqShape {
+  int nchunks, mtiles, gs, mgroups, units;
+};
+__device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped) {
+  ReqShape r;
+  r.nchunks = max(1, (L + CHUNK - 1) / CHUNK);
+  r.mtiles = (qlen * G + 15) / 16;
+  r.gs = grouped ? (r.mtiles >= 3 ? 4 : (r.mtiles == 2 ? 2 : 1)) : 1;
+  r.mgroups = (r.mtiles + r.gs - 1) / r.gs;
+  r.units = (qlen < 1 || qlen > qmax) ? 0 : r.nchunks * Hkv * r.mgroups;
+  return r;
 }
 
 // ------------------------------------------------------------------------------------------------------
 // plan: units per request, exclusive prefix sum, units per CTA
 // ------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_lens,
-                                                   int num_seqs, int G, int Hkv, int qmax, int nctas,
+                                                   int num_seqs, int G, int Hkv, int qmax, int grouped, int nctas,
                                                    int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
   __shared__ int s_warp[8];
   __shared__ int s_carry;
@@ -183,10 +202,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
   for (int base = 0; base < num_seqs; base += 256) {
     const int r = base + tid;
     int u = 0;
-    if (r < num_seqs) {
-      int nc, mt;
-      u = units_of(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, nc, mt);
-    }
+    if (r < num_seqs) u = req_shape(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, grouped).units;
     int x = u;  // inclusive scan inside the warp
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -214,56 +230,247 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
 // ------------------------------------------------------------------------------------------------------
 // main kernel
 // ------------------------------------------------------------------------------------------------------
-template <int D>
+// Warps of a CTA are organised in groups of GS warps (GS = 1, 2 or 4, chosen per request from its number of
+// 16-row m tiles). A group streams its own 32-key chunks through its own slice of the TMA ring; inside a group
+// every warp reads the same K/V stage from shared memory and works on its own m tile, so K/V bytes are fetched
+// from HBM once however many query rows use them. GS = 1 (decode: all rows of a kv head fit one m tile) gives
+// four independent streams per CTA; GS = 4 (e.g. 8 query tokens x 7 heads = 56 rows) gives one stream feeding
+// four m tiles. Groups that worked on the same m tile are combined through shared memory at the end of an item.
+template <int D, bool ROWS16>
 struct Geom {
   static constexpr int TILE = CHUNK * D;          // one K or V chunk
   static constexpr int STAGE = 2 * TILE;          // K chunk + V chunk
-  static constexpr int RING = NWARPS * NSTAGE * STAGE;
+  static constexpr int NSTG = NWARPS * NSTAGE;    // stages per CTA
+  static constexpr int RING = NSTG * STAGE;
+  static constexpr int SLOTS = ROWS16 ? NWARPS : 1;  // m tiles a CTA can hold q for
   static constexpr int QROW = D + 16;             // s_q row stride: conflict-free A-fragment loads
   static constexpr int ACC_RS = D + 8;            // combine buffer row stride in floats
-  static constexpr int SMALL = 16 * QROW + (32 + 2 * NWARPS * 16 + 32) * 4;
+  static constexpr int SMALL = SLOTS * 16 * QROW + 6 * 64 * 4;
   static constexpr int SMEM = 1024 + RING + SMALL;  // 1024: manual alignment of the ring
   static_assert(NWARPS * 16 * ACC_RS * 4 <= RING, "combine buffer aliases the ring");
 };
 
+// q fold + quantize for the 16 rows of m tile `mt` of (request, kv head); all 128 threads, 8 per row.
+// The reference's implementation B does this in double (exact products q * s_k, scale = max / 127, division).
+// FP64 issue is slow enough on this part to cost microseconds per item, so the same values are carried as
+// unevaluated fp32 pairs (~2^-46); only exact rounding ties take the literal double route.
+template <int D>
+__device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, float* s_chi, float* s_clo, int tok,
+                                           int qlen, int kvh, int mt, int tid) {
+  constexpr int CPT = D / 8, QROW = D + 16;
+  const int row = tid >> 3, part = tid & 7, d0 = part * CPT;
+  const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+  float x[CPT];   // fp32(q * s_k): what gets quantized
+  ff amax = {0.f, 0.f};
+#pragma unroll
+  for (int e = 0; e < CPT; ++e) x[e] = 0.f;
+  float sk[CPT];   // vector loads issued up front: scalar loads inside the loop would serialize on L2 latency
+#pragma unroll
+  for (int v4 = 0; v4 < CPT / 4; ++v4) {
+    const float4 t4 = a.pc_k ? __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0) + v4)
+                             : make_float4(1.f, 1.f, 1.f, 1.f);
+    sk[4 * v4] = t4.x, sk[4 * v4 + 1] = t4.y, sk[4 * v4 + 2] = t4.z, sk[4 * v4 + 3] = t4.w;
+  }
+  if (rt < qlen) {
+    const __nv_bfloat16* qp = a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0;
+#pragma unroll
+    for (int v8 = 0; v8 < CPT / 8; ++v8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(qp + 8 * v8);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) x[8 * v8 + 2 * k] = bf16lo(w[k]), x[8 * v8 + 2 * k + 1] = bf16hi(w[k]);
+    }
+#pragma unroll
+    for (int e = 0; e < CPT; ++e) {
+      const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo (sk = 1 for a per-head K scale)
+      x[e] = p.hi;
+      amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
+    }
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1)
+    amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
+  // sq = max(amax / 127, 1e-8)
+  ff sq;
+  {
+    const float q1 = __fdiv_rn(amax.hi, 127.f);
+    const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
+    sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
+    constexpr float E_HI = 1e-8f;
+    const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
+    if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
+  }
+  uint32_t w[CPT / 4];
+#pragma unroll
+  for (int k = 0; k < CPT / 4; ++k) {
+    int b[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
+      // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
+      // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
+      const float xe = x[4 * k + e];
+      const float qf = __fdiv_rn(xe, sq.hi);
+      int r = __float2int_rn(qf);
+      if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-3f) {
+        const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
+        r = __double2int_rn(static_cast<double>(xe) / sqd);
+      }
+      b[e] = max(-127, min(127, r));
+    }
+    w[k] = pack4(b[0], b[1], b[2], b[3]);
+  }
+  if constexpr (CPT == 16)
+    *reinterpret_cast<uint4*>(&s_q[row * QROW + d0]) = make_uint4(w[0], w[1], w[2], w[3]);
+  else
+    *reinterpret_cast<uint2*>(&s_q[row * QROW + d0]) = make_uint2(w[0], w[1]);
+  if (part == 0) {
+    // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
+    ff c = sq;
+    if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
+    c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
+    s_chi[row] = c.hi;
+    s_clo[row] = c.lo;
+  }
+}
+
+// Per-warp state of one m tile: q fragments, score scales, causal limits, running softmax statistics, output.
+template <int D, bool ROWS16>
+struct TileState {
+  uint32_t qa[D / 32][4];
+  float ch0, cl0, ch1, cl1;
+  int lim0, lim1;
+  float m0, m1, l0, l1;
+  float acc[D / 8][ROWS16 ? 4 : 2];
+};
+
+// One 32-key chunk: S = Q.K^T, online softmax, P -> int8, O += P.V. sk / sv: shared-memory addresses of the
+// swizzled K and V tiles; n_base: absolute position of the chunk's first key.
+template <int D, bool ROWS16>
+__device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk, uint32_t sv, int n_base, int lim_all,
+                                           int krow, int kmat, int vrow, int t) {
+  constexpr int KSTEPS = D / 32, NT = D / 8;
+  // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
+  int sacc[4][4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
+#pragma unroll
+    for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
+      uint32_t b[4];
+      ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat));
+      mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
+      mma_s8(sacc[j], s.qa[2 * s2 + 1], b[2], b[3]);
+    }
+  }
+  // accumulator (j, e) of lane (g, t): row g (e < 2) or g + 8, key n_base + 8j + 2t + (e & 1)
+  const bool need_mask = n_base + CHUNK > lim_all;
+  float p0[8], p1[8];
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < 4; ++j)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int n = n_base + 8 * j + 2 * t + e;
+      p0[2 * j + e] = (!need_mask || n < s.lim0) ? score(sacc[j][e], s.ch0, s.cl0) : -INFINITY;
+      mx0 = fmaxf(mx0, p0[2 * j + e]);
+      if (ROWS16) {
+        p1[2 * j + e] = (!need_mask || n < s.lim1) ? score(sacc[j][2 + e], s.ch1, s.cl1) : -INFINITY;
+        mx1 = fmaxf(mx1, p1[2 * j + e]);
+      }
+    }
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  const float mn0 = fmaxf(s.m0, mx0), nb0 = -mn0 * LOG2E;
+  // m0 == mn0 also covers the "nothing seen yet" sentinel, where the fma below would see -1e30 * LOG2E cancel badly
+  const float al0 = (s.m0 == mn0) ? 1.f : ex2(fmaf(s.m0, LOG2E, nb0));
+  // the tile maximum of P is pexp(mx): the same instructions compute every P below, and they are monotonic
+  const float ps0 = fmaxf(ex2(fmaf(mx0, LOG2E, nb0)) * (1.f / 127.f), 1e-30f);
+  const float ri0 = __frcp_rn(ps0);
+  int q0[8], qs0 = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    q0[k] = min(__float2int_rn(ex2(fmaf(p0[k], LOG2E, nb0)) * ri0), 127);
+    qs0 += q0[k];
+  }
+  float al1 = 1.f, ps1 = 0.f;
+  int q1[8], qs1 = 0;
+  if (ROWS16) {
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn1 = fmaxf(s.m1, mx1), nb1 = -mn1 * LOG2E;
+    al1 = (s.m1 == mn1) ? 1.f : ex2(fmaf(s.m1, LOG2E, nb1));
+    ps1 = fmaxf(ex2(fmaf(mx1, LOG2E, nb1)) * (1.f / 127.f), 1e-30f);
+    const float ri1 = __frcp_rn(ps1);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      q1[k] = min(__float2int_rn(ex2(fmaf(p1[k], LOG2E, nb1)) * ri1), 127);
+      qs1 += q1[k];
+    }
+    s.m1 = mn1;
+    qs0 |= qs1 << 16;  // both row sums (each < 2^13) through one pair of shuffles
+  }
+  s.m0 = mn0;
+  qs0 += __shfl_xor_sync(0xffffffffu, qs0, 1);
+  qs0 += __shfl_xor_sync(0xffffffffu, qs0, 2);
+  if (ROWS16) {
+    s.l1 = s.l1 * al1 + static_cast<float>(qs0 >> 16) * ps1;
+    qs0 &= 0xffff;
+  }
+  s.l0 = s.l0 * al0 + static_cast<float>(qs0) * ps0;
+  // P as the A operand of the PV mma: k slots 4t..4t+3 <- keys {2t, 2t+1, 8+2t, 9+2t}, slots 16+.. <- +16
+  uint32_t pa[4];
+  pa[0] = pack4(q0[0], q0[1], q0[2], q0[3]);
+  pa[2] = pack4(q0[4], q0[5], q0[6], q0[7]);
+  pa[1] = ROWS16 ? pack4(q1[0], q1[1], q1[2], q1[3]) : 0u;
+  pa[3] = ROWS16 ? pack4(q1[4], q1[5], q1[6], q1[7]) : 0u;
+
+  // O += P.V: 16 channels (two n-tiles) per transposing ldmatrix
+#pragma unroll
+  for (int jp = 0; jp < NT / 2; ++jp) {
+    uint32_t b[4];
+    ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp));
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      int pacc[4] = {0, 0, 0, 0};
+      mma_s8(pacc, pa, b[h2], b[2 + h2]);
+      float* o = s.acc[2 * jp + h2];
+      o[0] = o[0] * al0 + static_cast<float>(pacc[0]) * ps0;
+      o[1] = o[1] * al0 + static_cast<float>(pacc[1]) * ps0;
+      if (ROWS16) {
+        o[2] = o[2] * al1 + static_cast<float>(pacc[2]) * ps1;
+        o[3] = o[3] * al1 + static_cast<float>(pacc[3]) * ps1;
+      }
+    }
+  }
+}
+
 template <int D, bool ROWS16>
 __global__ void __launch_bounds__(NTHREADS, 2)
     decode_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
-  using Gm = Geom<D>;
-  constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS;
+  using Gm = Geom<D, ROWS16>;
+  constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS, NSTG = Gm::NSTG;
   constexpr int NROWS = ROWS16 ? 16 : 8;
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[NWARPS * NSTAGE];
+  __shared__ __align__(8) uint64_t s_full[NSTG];    // TMA landed in the stage
+  __shared__ __align__(8) uint64_t s_empty[NSTG];   // every warp of the group is done with the stage
   __shared__ int s_req;
 
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
-  int8_t* s_q = reinterpret_cast<int8_t*>(ring_ptr + Gm::RING);
-  float* s_chi = reinterpret_cast<float*>(ring_ptr + Gm::RING + 16 * QROW);  // [16] score scale, high part
-  float* s_clo = s_chi + 16;            // [16] score scale, low part
-  float* s_m = s_clo + 16;              // [NWARPS][16]
-  float* s_l = s_m + NWARPS * 16;       // [NWARPS][16]
-  float* s_M = s_l + NWARPS * 16;       // [16] combined max
-  float* s_inv = s_M + 16;              // [16] 1 / combined denominator (direct) or denominator (partial)
+  int8_t* s_q = reinterpret_cast<int8_t*>(ring_ptr + Gm::RING);                       // [SLOTS][16][QROW]
+  float* s_chi = reinterpret_cast<float*>(ring_ptr + Gm::RING + Gm::SLOTS * 16 * QROW);  // [64] score scale, high part
+  float* s_clo = s_chi + 64;            // [64] score scale, low part
+  float* s_m = s_clo + 64;              // [NWARPS][16] running max per warp
+  float* s_l = s_m + 64;                // [NWARPS][16] denominator per warp
+  float* s_M = s_l + 64;                // [slot][16] combined max
+  float* s_inv = s_M + 64;              // [slot][16] 1 / combined denominator (whole item) or the denominator (cut item)
   float* s_acc = reinterpret_cast<float*>(ring_ptr);  // [NWARPS][NROWS][ACC_RS], valid between chunk loops
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int total = a.hdr[1], W = a.hdr[2];
   const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
   if (ubeg >= uend) return;
-
-  if (tid == 0) {
-#pragma unroll
-    for (int i = 0; i < NWARPS * NSTAGE; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  fence_proxy_async();
-  __syncthreads();
-
-  const uint32_t wring = ring + warp * NSTAGE * Gm::STAGE;
-  const uint32_t wbar = smem_u32(&s_bar[warp * NSTAGE]);
-  uint32_t gbase = 0;  // chunks this warp has pushed through its ring so far (stage and phase bookkeeping)
-  bool ok = true;
 
   // Lane-constant pieces of the ldmatrix addresses.
   // K (non-transposed, 4 matrices of 8 keys x 16 channels): lane l addresses key (l & 7) of matrix l >> 3.
@@ -272,6 +479,9 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int krow = lane & 7, kmat = lane >> 3;
   const int vrow = (lane & 1) + 8 * ((lane >> 1) & 1) + 2 * ((lane >> 2) & 3) + 16 * (lane >> 4);
 
+  int cur_gs = 0;      // group size the barriers are currently initialised for (0: not yet)
+  int cst = 0, cpass = 0;  // consumer position of this warp's group in its ring: stage, completed passes
+  bool ok = true;
   int u = ubeg;
   bool first_seg = true;
   KVQ_TL(0);
@@ -283,42 +493,72 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     const int req = s_req;
     KVQ_TL(1);
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
-    int nchunks, mtiles;
-    units_of(qlen, L, a.G, a.Hkv, a.qmax, nchunks, mtiles);
+    const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped);
+    const int nchunks = rs.nchunks;
     const int p0 = a.prefix[req], p1 = a.prefix[req + 1];
     const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
 
-    // ---- items (kv head, m tile) of this request that intersect [u, uend) ----
+    // ---- warp groups for this request; the ring and its barriers are re-partitioned when the group size changes
+    //      (everything issued so far has been consumed at this point) ----
+    const int GS = rs.gs, lgs = GS >> 1 /* log2 of 1, 2, 4 */, NG = NWARPS >> lgs, gidx = warp >> lgs,
+              msl = warp & (GS - 1), RD = NSTAGE * GS;
+    if (GS != cur_gs) {
+      if (tid == 0) {
+        for (int i = 0; i < NSTG; ++i) {
+          if (cur_gs != 0) mbar_inval(smem_u32(&s_full[i])), mbar_inval(smem_u32(&s_empty[i]));
+          mbar_init(smem_u32(&s_full[i]), 1);
+          mbar_init(smem_u32(&s_empty[i]), GS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      }
+      fence_proxy_async();
+      __syncthreads();
+      cur_gs = GS;
+      cst = 0, cpass = 0;
+    }
+    const uint32_t gring = ring + gidx * RD * Gm::STAGE;
+    const uint32_t gfull = smem_u32(&s_full[gidx * RD]), gempty = smem_u32(&s_empty[gidx * RD]);
+
+    // ---- items (kv head, m-tile group) of this request that intersect [u, uend) ----
     while (u < uend && u < p1) {
       const int item = (u - p0) / nchunks, c0 = (u - p0) - item * nchunks;
-      const int kvh = item / mtiles, mt = item - kvh * mtiles;
+      const int kvh = item / rs.mgroups, mg = item - kvh * rs.mgroups;
       const int c1 = min(nchunks, c0 + (uend - u));
       const bool whole = (c0 == 0 && c1 == nchunks);
-      const int nw = (c1 - c0 - warp + NWARPS - 1) / NWARPS;  // chunks of this warp: c0 + warp + NWARPS * i
+      // the group consumes chunks c0 + gidx + NG * i, i < nig; inside the group warp msl produces i = msl + GS * ip
+      const int nig = (c1 - c0 - gidx + NG - 1) / NG;
+      const int npw = (nig - msl + GS - 1) >> lgs;
+      const int mtw = mg * GS + msl;                 // this warp's m tile
+      const bool active = mtw < rs.mtiles;
 
-      // -- TMA producer (per warp): page ids 16 chunks at a time, one lane per 16-key half chunk --
+      // -- TMA producer: page ids 16 chunks at a time, one lane per 16-key half chunk --
       int pg_cur = 0, pg_next = 0;
+      auto chunk_of = [&](int ip) { return c0 + gidx + NG * (msl + GS * ip); };
       auto load_pages = [&](int batch) {
-        const int i = 16 * batch + (lane >> 1);
+        const int ip = 16 * batch + (lane >> 1);
         int pg = 0;
-        if (i < nw) {
-          const int c = c0 + warp + NWARPS * i;
+        if (ip < npw) {
+          const int c = chunk_of(ip);
           const int n0 = c * CHUNK + (lane & 1) * 16;
           pg = bt[(n0 < L ? n0 : c * CHUNK) >> a.lbs];
         }
         return pg;
       };
-      auto issue = [&](int i) {
-        if ((i & 15) == 0) {
-          pg_cur = (i == 0) ? load_pages(0) : pg_next;
-          pg_next = load_pages((i >> 4) + 1);
+      // dist: how far ahead of the consumer position (in the group's chunk sequence) the chunk lies, < RD
+      auto issue = [&](int ip, int dist) {
+        if ((ip & 15) == 0) {
+          pg_cur = (ip == 0) ? load_pages(0) : pg_next;
+          pg_next = load_pages((ip >> 4) + 1);
         }
-        const int pa = __shfl_sync(0xffffffffu, pg_cur, 2 * (i & 15));
-        const int pb = __shfl_sync(0xffffffffu, pg_cur, 2 * (i & 15) + 1);
-        if (lane == 0) {
-          const uint32_t gi = gbase + i, st = gi % NSTAGE;
-          const uint32_t bar = wbar + st * 8, dst = wring + st * Gm::STAGE;
-          const int c = c0 + warp + NWARPS * i;
+        const int pa = __shfl_sync(0xffffffffu, pg_cur, 2 * (ip & 15));
+        const int pb = __shfl_sync(0xffffffffu, pg_cur, 2 * (ip & 15) + 1);
+        int st = cst + dist, prev_pass = cpass - 1;   // pass in which the stage was last used
+        if (st >= RD) st -= RD, prev_pass = cpass;
+        if (GS > 1 && prev_pass >= 0)   // the other warps of the group must have left the stage's previous contents
+          ok = ok && __all_sync(0xffffffffu, mbar_wait(gempty + st * 8, prev_pass & 1));
+        if (lane == 0 && ok) {
+          const uint32_t bar = gfull + st * 8, dst = gring + st * Gm::STAGE;
+          const int c = chunk_of(ip);
           mbar_expect_tx(bar, Gm::STAGE);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
@@ -333,267 +573,101 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           }
         }
       };
-      int issued = 0;
       if (ok)
-        for (; issued < min(nw, NSTAGE - 1); ++issued) issue(issued);
+        for (int ip = 0; ip < min(npw, NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
       KVQ_TL(2);
 
-      // -- q prologue: fold s_k, quantize per row; 8 threads per row. The reference's implementation B does this
-      //    in double (exact products q * s_k, scale = max / 127, division). FP64 issue is slow enough on this part
-      //    to cost microseconds per item, so the same values are carried as unevaluated fp32 pairs (~2^-46). --
-      {
-        constexpr int CPT = D / 8;
-        const int row = tid >> 3, part = tid & 7, d0 = part * CPT;
-        const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-        float x[CPT];   // fp32(q * s_k): what gets quantized
-        ff amax = {0.f, 0.f};
-#pragma unroll
-        for (int e = 0; e < CPT; ++e) x[e] = 0.f;
-        float sk[CPT];   // vector loads issued up front: scalar loads inside the loop would serialize on L2 latency
-#pragma unroll
-        for (int v4 = 0; v4 < CPT / 4; ++v4) {
-          const float4 t4 = a.pc_k ? __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0) + v4)
-                                   : make_float4(1.f, 1.f, 1.f, 1.f);
-          sk[4 * v4] = t4.x, sk[4 * v4 + 1] = t4.y, sk[4 * v4 + 2] = t4.z, sk[4 * v4 + 3] = t4.w;
-        }
-        if (rt < qlen) {
-          const __nv_bfloat16* qp = a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0;
-#pragma unroll
-          for (int v8 = 0; v8 < CPT / 8; ++v8) {
-            const uint4 raw = *reinterpret_cast<const uint4*>(qp + 8 * v8);
-            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) x[8 * v8 + 2 * k] = bf16lo(w[k]), x[8 * v8 + 2 * k + 1] = bf16hi(w[k]);
-          }
-#pragma unroll
-          for (int e = 0; e < CPT; ++e) {
-            const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo (sk = 1 for a per-head K scale)
-            x[e] = p.hi;
-            amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
-          }
-        }
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1)
-          amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
-        // sq = max(amax / 127, 1e-8)
-        ff sq;
-        {
-          const float q1 = __fdiv_rn(amax.hi, 127.f);
-          const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
-          sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
-          constexpr float E_HI = 1e-8f;
-          const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
-          if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
-        }
-        uint32_t w[CPT / 4];
-#pragma unroll
-        for (int k = 0; k < CPT / 4; ++k) {
-          int b[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
-            // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
-            // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
-            const float xe = x[4 * k + e];
-            const float qf = __fdiv_rn(xe, sq.hi);
-            int r = __float2int_rn(qf);
-            if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-3f) {
-              const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
-              r = __double2int_rn(static_cast<double>(xe) / sqd);
-            }
-            b[e] = max(-127, min(127, r));
-          }
-          w[k] = pack4(b[0], b[1], b[2], b[3]);
-        }
-        if constexpr (CPT == 16)
-          *reinterpret_cast<uint4*>(&s_q[row * QROW + d0]) = make_uint4(w[0], w[1], w[2], w[3]);
-        else
-          *reinterpret_cast<uint2*>(&s_q[row * QROW + d0]) = make_uint2(w[0], w[1]);
-        if (part == 0) {
-          // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
-          ff c = sq;
-          if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
-          c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
-          s_chi[row] = c.hi;
-          s_clo[row] = c.lo;
-        }
-      }
+      // -- q prologue for every m tile of the group --
+      for (int sl = 0; sl < GS; ++sl)
+        if (mg * GS + sl < rs.mtiles)
+          q_prologue<D>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh, mg * GS + sl, tid);
       __syncthreads();
-      uint32_t qa[KSTEPS][4];
+      TileState<D, ROWS16> ts;
+      {
+        const int8_t* q_t = s_q + msl * 16 * QROW;
 #pragma unroll
-      for (int s = 0; s < KSTEPS; ++s) {
-        qa[s][0] = *reinterpret_cast<const uint32_t*>(&s_q[g * QROW + 32 * s + 4 * t]);
-        qa[s][2] = *reinterpret_cast<const uint32_t*>(&s_q[g * QROW + 32 * s + 16 + 4 * t]);
-        qa[s][1] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&s_q[(g + 8) * QROW + 32 * s + 4 * t]) : 0u;
-        qa[s][3] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&s_q[(g + 8) * QROW + 32 * s + 16 + 4 * t]) : 0u;
+        for (int s = 0; s < KSTEPS; ++s) {
+          ts.qa[s][0] = *reinterpret_cast<const uint32_t*>(&q_t[g * QROW + 32 * s + 4 * t]);
+          ts.qa[s][2] = *reinterpret_cast<const uint32_t*>(&q_t[g * QROW + 32 * s + 16 + 4 * t]);
+          ts.qa[s][1] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&q_t[(g + 8) * QROW + 32 * s + 4 * t]) : 0u;
+          ts.qa[s][3] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&q_t[(g + 8) * QROW + 32 * s + 16 + 4 * t]) : 0u;
+        }
+        ts.ch0 = s_chi[msl * 16 + g], ts.cl0 = s_clo[msl * 16 + g];
+        ts.ch1 = s_chi[msl * 16 + g + 8], ts.cl1 = s_clo[msl * 16 + g + 8];
+        // causal key limit per row: key n is visible iff n < L - qlen + 1 + (query token of the row)
+        auto row_lim = [&](int r) {
+          const int rt = (mtw * 16 + r) / a.G;
+          return rt < qlen ? L - qlen + 1 + rt : L;
+        };
+        ts.lim0 = row_lim(g), ts.lim1 = row_lim(g + 8);
+        ts.m0 = ts.m1 = -1e30f, ts.l0 = ts.l1 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+          for (int e = 0; e < (ROWS16 ? 4 : 2); ++e) ts.acc[j][e] = 0.f;
       }
-      const float ch0 = s_chi[g], cl0 = s_clo[g], ch1 = s_chi[g + 8], cl1 = s_clo[g + 8];
-      // causal key limit per row: key n is visible iff n < L - qlen + 1 + (query token of the row)
-      auto row_lim = [&](int r) {
-        const int rt = (mt * 16 + r) / a.G;
-        return rt < qlen ? L - qlen + 1 + rt : L;
-      };
-      const int lim0 = row_lim(g), lim1 = row_lim(g + 8);
       const int lim_all = L - qlen + 1;  // every row sees keys below this
       KVQ_TL(3);
 
-      float m0 = -1e30f, m1 = -1e30f, l0 = 0.f, l1 = 0.f;
-      float acc[NT][ROWS16 ? 4 : 2];
-#pragma unroll
-      for (int j = 0; j < NT; ++j)
-#pragma unroll
-        for (int e = 0; e < (ROWS16 ? 4 : 2); ++e) acc[j][e] = 0.f;
-
-      // -- main loop over this warp's chunks --
-      for (int i = 0; i < nw && ok; ++i) {
-        if (issued < nw) issue(issued++);
-        const uint32_t gi = gbase + i, st = gi % NSTAGE;
-        ok = __all_sync(0xffffffffu, mbar_wait(wbar + st * 8, (gi / NSTAGE) & 1));
+      // -- main loop over the group's chunks --
+      for (int i = 0; i < nig && ok; ++i) {
+        const int ipn = (i >> lgs) + NSTAGE - 1;       // keep NSTAGE - 1 of my chunks in flight
+        if ((i & (GS - 1)) == msl && ipn < npw) issue(ipn, (NSTAGE - 1) * GS);
+        const int st = cst;
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(gfull + st * 8, cpass & 1));
         if (!ok) break;
         if (i == 0) KVQ_TL(4);
-        const uint32_t sk = wring + st * Gm::STAGE, sv = sk + Gm::TILE;
-        const int n_base = (c0 + warp + NWARPS * i) * CHUNK;
-
-        // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
-        int sacc[4][4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
-#pragma unroll
-          for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
-            uint32_t b[4];
-            ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat));
-            mma_s8(sacc[j], qa[2 * s2], b[0], b[1]);
-            mma_s8(sacc[j], qa[2 * s2 + 1], b[2], b[3]);
-          }
+        if (active) {
+          const uint32_t sk = gring + st * Gm::STAGE;
+          chunk_step<D, ROWS16>(ts, sk, sk + Gm::TILE, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t);
         }
-        // accumulator (j, e) of lane (g, t): row g (e < 2) or g + 8, key n_base + 8j + 2t + (e & 1)
-        const bool need_mask = n_base + CHUNK > lim_all;
-        float p0[8], p1[8];
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int n = n_base + 8 * j + 2 * t + e;
-            p0[2 * j + e] = (!need_mask || n < lim0) ? score(sacc[j][e], ch0, cl0) : -INFINITY;
-            mx0 = fmaxf(mx0, p0[2 * j + e]);
-            if (ROWS16) {
-              p1[2 * j + e] = (!need_mask || n < lim1) ? score(sacc[j][2 + e], ch1, cl1) : -INFINITY;
-              mx1 = fmaxf(mx1, p1[2 * j + e]);
-            }
-          }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        const float mn0 = fmaxf(m0, mx0), nb0 = -mn0 * LOG2E;
-        // m0 == mn0 also covers the "nothing seen yet" sentinel, where the fma below would see -1e30 * LOG2E cancel badly
-        const float al0 = (m0 == mn0) ? 1.f : ex2(fmaf(m0, LOG2E, nb0));
-        // the tile maximum of P is pexp(mx): the same instructions compute every P below, and they are monotonic
-        const float ps0 = fmaxf(ex2(fmaf(mx0, LOG2E, nb0)) * (1.f / 127.f), 1e-30f);
-        const float ri0 = __frcp_rn(ps0);
-        int q0[8], qs0 = 0;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          q0[k] = min(__float2int_rn(ex2(fmaf(p0[k], LOG2E, nb0)) * ri0), 127);
-          qs0 += q0[k];
-        }
-        float al1 = 1.f, ps1 = 0.f;
-        int q1[8], qs1 = 0;
-        if (ROWS16) {
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-          mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-          const float mn1 = fmaxf(m1, mx1), nb1 = -mn1 * LOG2E;
-          al1 = (m1 == mn1) ? 1.f : ex2(fmaf(m1, LOG2E, nb1));
-          ps1 = fmaxf(ex2(fmaf(mx1, LOG2E, nb1)) * (1.f / 127.f), 1e-30f);
-          const float ri1 = __frcp_rn(ps1);
-#pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            q1[k] = min(__float2int_rn(ex2(fmaf(p1[k], LOG2E, nb1)) * ri1), 127);
-            qs1 += q1[k];
-          }
-          m1 = mn1;
-          qs0 |= qs1 << 16;  // both row sums (each < 2^13) through one pair of shuffles
-        }
-        m0 = mn0;
-        qs0 += __shfl_xor_sync(0xffffffffu, qs0, 1);
-        qs0 += __shfl_xor_sync(0xffffffffu, qs0, 2);
-        if (ROWS16) {
-          l1 = l1 * al1 + static_cast<float>(qs0 >> 16) * ps1;
-          qs0 &= 0xffff;
-        }
-        l0 = l0 * al0 + static_cast<float>(qs0) * ps0;
-        // P as the A operand of the PV mma: k slots 4t..4t+3 <- keys {2t, 2t+1, 8+2t, 9+2t}, slots 16+.. <- +16
-        uint32_t pa[4];
-        pa[0] = pack4(q0[0], q0[1], q0[2], q0[3]);
-        pa[2] = pack4(q0[4], q0[5], q0[6], q0[7]);
-        pa[1] = ROWS16 ? pack4(q1[0], q1[1], q1[2], q1[3]) : 0u;
-        pa[3] = ROWS16 ? pack4(q1[4], q1[5], q1[6], q1[7]) : 0u;
-
-        // O += P.V: 16 channels (two n-tiles) per transposing ldmatrix
-#pragma unroll
-        for (int jp = 0; jp < NT / 2; ++jp) {
-          uint32_t b[4];
-          ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp));
-#pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            int pacc[4] = {0, 0, 0, 0};
-            mma_s8(pacc, pa, b[h2], b[2 + h2]);
-            float* o = acc[2 * jp + h2];
-            o[0] = o[0] * al0 + static_cast<float>(pacc[0]) * ps0;
-            o[1] = o[1] * al0 + static_cast<float>(pacc[1]) * ps0;
-            if (ROWS16) {
-              o[2] = o[2] * al1 + static_cast<float>(pacc[2]) * ps1;
-              o[3] = o[3] * al1 + static_cast<float>(pacc[3]) * ps1;
-            }
-          }
-        }
-        __syncwarp();  // every lane is done with this stage before lane 0 refills it
+        __syncwarp();  // every lane is done with this stage before it is refilled
+        if (GS > 1 && lane == 0) mbar_arrive(gempty + st * 8);
+        if (++cst == RD) cst = 0, ++cpass;
       }
-      gbase += nw > 0 ? nw : 0;
       KVQ_TL(5);
       if (!ok) atomicExch(a.hdr, 1);
 
-      // -- combine the warps: weights exp2(m_w - M) --
+      // -- combine the warps that worked on the same m tile (slot msl of every group): weights exp(m_w - M) --
       if (t == 0) {
-        s_m[warp * 16 + g] = m0, s_l[warp * 16 + g] = l0;
-        s_m[warp * 16 + g + 8] = m1, s_l[warp * 16 + g + 8] = l1;
+        s_m[warp * 16 + g] = ts.m0, s_l[warp * 16 + g] = ts.l0;
+        s_m[warp * 16 + g + 8] = ts.m1, s_l[warp * 16 + g + 8] = ts.l1;
       }
       __syncthreads();  // also: every warp has left the ring, which s_acc aliases
       {
         float M0 = -1e30f, M1 = -1e30f;
-#pragma unroll
-        for (int w = 0; w < NWARPS; ++w) M0 = fmaxf(M0, s_m[w * 16 + g]), M1 = fmaxf(M1, s_m[w * 16 + g + 8]);
-        const float w0 = ex2((m0 - M0) * LOG2E), w1 = ex2((m1 - M1) * LOG2E);
+        for (int w = msl; w < NWARPS; w += GS) M0 = fmaxf(M0, s_m[w * 16 + g]), M1 = fmaxf(M1, s_m[w * 16 + g + 8]);
+        const float w0 = ex2((ts.m0 - M0) * LOG2E), w1 = ex2((ts.m1 - M1) * LOG2E);
         float* dst0 = s_acc + (warp * NROWS + g) * ACC_RS + 2 * t;
 #pragma unroll
         for (int j = 0; j < NT; ++j) {
-          *reinterpret_cast<float2*>(dst0 + 8 * j) = make_float2(acc[j][0] * w0, acc[j][1] * w0);
+          *reinterpret_cast<float2*>(dst0 + 8 * j) = make_float2(ts.acc[j][0] * w0, ts.acc[j][1] * w0);
           if (ROWS16)
             *reinterpret_cast<float2*>(dst0 + 8 * ACC_RS + 8 * j) =
-                make_float2(acc[j][ROWS16 ? 2 : 0] * w1, acc[j][ROWS16 ? 3 : 1] * w1);
+                make_float2(ts.acc[j][ROWS16 ? 2 : 0] * w1, ts.acc[j][ROWS16 ? 3 : 1] * w1);
         }
-        if (tid < 16) {
+        if (tid < GS * 16) {
+          const int sl = tid >> 4, r = tid & 15;
           float Mr = -1e30f, Lr = 0.f;
-#pragma unroll
-          for (int w = 0; w < NWARPS; ++w) Mr = fmaxf(Mr, s_m[w * 16 + tid]);
-#pragma unroll
-          for (int w = 0; w < NWARPS; ++w) Lr += s_l[w * 16 + tid] * ex2((s_m[w * 16 + tid] - Mr) * LOG2E);
+          for (int w = sl; w < NWARPS; w += GS) Mr = fmaxf(Mr, s_m[w * 16 + r]);
+          for (int w = sl; w < NWARPS; w += GS) Lr += s_l[w * 16 + r] * ex2((s_m[w * 16 + r] - Mr) * LOG2E);
           s_M[tid] = Mr;
           s_inv[tid] = whole ? 1.f / fmaxf(Lr, 1e-30f) : Lr;
         }
       }
       __syncthreads();
+      KVQ_TL(6);
 
       // -- epilogue: 4 channels per thread and step; s_v applied here --
-      KVQ_TL(6);
-      const int slot = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * PART_ROWS;
-      for (int i = tid; i < NROWS * (D / 4); i += NTHREADS) {
-        const int row = i / (D / 4), c4 = (i - row * (D / 4)) * 4;
-        const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-        if (rt >= qlen) continue;
+      const int slot_base = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * a.part_rows;
+      for (int i = tid; i < GS * NROWS * (D / 4); i += NTHREADS) {
+        const int sl = i / (NROWS * (D / 4)), rem = i - sl * (NROWS * (D / 4));
+        const int row = rem / (D / 4), c4 = (rem - row * (D / 4)) * 4;
+        const int mts = mg * GS + sl;
+        const int R = mts * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+        if (mts >= rs.mtiles || rt >= qlen) continue;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int w = 0; w < NWARPS; ++w) {
+        for (int w = sl; w < NWARPS; w += GS) {   // fixed order: deterministic
           const float4 x = *reinterpret_cast<const float4*>(s_acc + (w * NROWS + row) * ACC_RS + c4);
           v.x += x.x, v.y += x.y, v.z += x.z, v.w += x.w;
         }
@@ -605,24 +679,25 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           sv4 = make_float4(one, one, one, one);
         }
         if (whole) {
-          const float inv = s_inv[row];
+          const float inv = s_inv[sl * 16 + row];
           const uint2 o = make_uint2(pack_bf16x2(v.x * inv * sv4.x, v.y * inv * sv4.y),
                                      pack_bf16x2(v.z * inv * sv4.z, v.w * inv * sv4.w));
           *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + c4) = o;
         } else {
-          *reinterpret_cast<float4*>(a.part_acc + static_cast<int64_t>(slot + row) * D + c4) =
+          const int prow = slot_base + sl * 16 + row;
+          *reinterpret_cast<float4*>(a.part_acc + static_cast<int64_t>(prow) * D + c4) =
               make_float4(v.x * sv4.x, v.y * sv4.y, v.z * sv4.z, v.w * sv4.w);
           if (c4 == 0) {
-            a.part_ml[(slot + row) * 2] = s_M[row];
-            a.part_ml[(slot + row) * 2 + 1] = s_inv[row];
+            a.part_ml[prow * 2] = s_M[sl * 16 + row];
+            a.part_ml[prow * 2 + 1] = s_inv[sl * 16 + row];
           }
         }
       }
       // generic-proxy writes to the ring (s_acc) come before the next item's TMA writes
       fence_proxy_async();
       __syncthreads();
-      u += c1 - c0;
       KVQ_TL(7);
+      u += c1 - c0;
       first_seg = false;
     }
   }
@@ -656,17 +731,17 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   __syncthreads();
   const int req = s_req;
   const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok;
-  int nchunks, mtiles;
-  units_of(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, nchunks, mtiles);
-  const int p0 = a.prefix[req];
-  const int item = (u - p0) / nchunks, kvh = item / mtiles, mt = item - kvh * mtiles;
+  const ReqShape rs = req_shape(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, a.grouped);
+  const int nchunks = rs.nchunks, p0 = a.prefix[req];
+  const int item = (u - p0) / nchunks, kvh = item / rs.mgroups, mg = item - kvh * rs.mgroups;
   const int A = p0 + item * nchunks, B = A + nchunks;
   const int c_lo = A / W, c_hi = (B - 1) / W;
   if (A == u || c_lo != static_cast<int>(blockIdx.x)) return;  // not cut here, or an earlier boundary merges it
-  const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-  if (rt >= qlen) return;
+  const int mts = mg * rs.gs + (row >> 4);   // partial row = (m tile of the group) * 16 + row of the tile
+  const int R = mts * 16 + (row & 15), rt = R / a.G, rh = R - rt * a.G;
+  if ((row >> 4) >= rs.gs || mts >= rs.mtiles || rt >= qlen) return;
   // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
-  auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * PART_ROWS + row; };
+  auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
   const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
 
   float M = -1e30f;
@@ -741,8 +816,8 @@ std::vector<MapEntry> g_maps;
 
 template <int D, bool R16>
 int prepare_variant(int& occ) {
-  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D>::SMEM));
-  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel<D, R16>, NTHREADS, Geom<D>::SMEM));
+  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D, R16>::SMEM));
+  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel<D, R16>, NTHREADS, Geom<D, R16>::SMEM));
   occ = std::max(1, std::min(occ, MAX_CTAS_PER_SM));
   return KVQ_OK;
 }
@@ -829,12 +904,12 @@ size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 struct WorkspaceLayout {
   size_t prefix, part_acc, part_ml, total;
 };
-WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas) {
+WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas, int part_rows) {
   WorkspaceLayout w;
   w.prefix = HDR_BYTES;
   w.part_acc = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
-  w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * PART_ROWS * D * 4;
-  w.total = w.part_ml + static_cast<size_t>(max_ctas) * 2 * PART_ROWS * 2 * 4;
+  w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * part_rows * D * 4;
+  w.total = w.part_ml + static_cast<size_t>(max_ctas) * 2 * part_rows * 2 * 4;
   return w;
 }
 
@@ -846,7 +921,8 @@ using namespace kvq;
 extern "C" __attribute__((visibility("default"))) size_t kvq_decode_workspace_size(int num_seqs, int head_dim) {
   DeviceInfo* di = nullptr;
   if (num_seqs < 0 || (head_dim != 64 && head_dim != 128) || device_info(&di) != KVQ_OK) return 0;
-  return workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM).total;
+  // sized for the grouped mode (multi-token queries); single-token decode needs a quarter of the partial area
+  return workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM, PART_ROWS_GROUPED).total;
 }
 
 extern "C" __attribute__((visibility("default"))) int kvq_decode_status(const void* workspace, int* status, kvq_stream_t stream) {
@@ -890,7 +966,13 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   const bool rows16 = G * max_q > 8;
   const int occ = di->occ[head_dim == 128][rows16];
   const int grid = di->sms * occ;
-  const WorkspaceLayout wl = workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM);
+  // Multi-token queries with more than one m tile per kv head share K/V streams between warps (grouped mode); its
+  // partial area is four times larger, so a workspace that only fits the plain layout falls back to one m tile
+  // per item (same results, K/V re-read per m tile).
+  const int mtiles_max = (G * max_q + 15) / 16;
+  WorkspaceLayout wl = workspace_layout(num_seqs, head_dim, grid, PART_ROWS_GROUPED);
+  int grouped = rows16 && mtiles_max >= 2 && workspace_bytes >= wl.total;
+  if (!grouped) wl = workspace_layout(num_seqs, head_dim, grid, PART_ROWS);
   if (!workspace || workspace_bytes < wl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
     set_error("decode workspace: need %zu bytes aligned to 256, got %zu at %p", wl.total, workspace_bytes, workspace);
     return KVQ_ERR_WORKSPACE;
@@ -912,6 +994,7 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   a.bs_mask = block_size - 1;
   a.q_st = q_stride_t, a.q_sh = q_stride_h, a.o_st = o_stride_t, a.o_sh = o_stride_h, a.bt_stride = bt_stride;
   a.pc_k = k_per_channel, a.pc_v = v_per_channel;
+  a.grouped = grouped, a.part_rows = grouped ? PART_ROWS_GROUPED : PART_ROWS;
   CUtensorMap tm_k, tm_v;
   if ((rc = cache_tensor_map(k_cache, num_blocks, block_size, num_kv_heads, head_dim, kc_stride_b, kc_stride_n,
                              kc_stride_h, &tm_k, a.kpos)) != KVQ_OK)
@@ -921,23 +1004,23 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     return rc;
 
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grid, a.hdr,
+  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, grid, a.hdr,
                                 reinterpret_cast<int32_t*>(ws + wl.prefix));
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   if (head_dim == 128) {
     if (rows16)
-      decode_kernel<128, true><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
+      decode_kernel<128, true><<<grid, NTHREADS, Geom<128, true>::SMEM, s>>>(a, tm_k, tm_v);
     else
-      decode_kernel<128, false><<<grid, NTHREADS, Geom<128>::SMEM, s>>>(a, tm_k, tm_v);
+      decode_kernel<128, false><<<grid, NTHREADS, Geom<128, false>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, a.part_rows), MERGE_THREADS, 0, s>>>(a);
   } else {
     if (rows16)
-      decode_kernel<64, true><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
+      decode_kernel<64, true><<<grid, NTHREADS, Geom<64, true>::SMEM, s>>>(a, tm_k, tm_v);
     else
-      decode_kernel<64, false><<<grid, NTHREADS, Geom<64>::SMEM, s>>>(a, tm_k, tm_v);
+      decode_kernel<64, false><<<grid, NTHREADS, Geom<64, false>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, a.part_rows), MERGE_THREADS, 0, s>>>(a);
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
@@ -996,8 +1079,11 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_
     int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
     int k_per_channel, int v_per_channel, int max_query_len, int qmax, kvq_stream_t stream) {
   if (num_seqs > 0 && (head_dim == 64 || head_dim == 128)) {
-    const size_t need = kvq_decode_workspace_size(num_seqs, head_dim);
-    if (need == 0) return KVQ_ERR_CUDA;  // message already set
+    // the plain layout (one m tile per item) is enough: with it the call never needs more than this
+    DeviceInfo* di = nullptr;
+    const int rc0 = device_info(&di);
+    if (rc0 != KVQ_OK) return rc0;
+    const size_t need = workspace_layout(num_seqs, head_dim, di->sms * MAX_CTAS_PER_SM, PART_ROWS).total;
     if (need > KVQ_STATIC_WS_BYTES) {
       set_error("kvq_int8_decode_attention_noalloc: %d requests need %zu bytes of scratch, the built-in array holds %zu; "
                 "use kvq_int8_decode_attention with a caller-provided workspace",

@@ -3,7 +3,7 @@
 It serves callers that cannot allocate device memory (all HBM already given to the KV pool, code running under
 someone else's allocator or graph capture), so it keeps its scratch in a fixed array inside the library. Here it
 is compared with the regular entry point, which gets a workspace from the caller: same kernels, so the outputs
-must be identical (checked with the tolerance the other GPU tests use, and for equality). Two calls in a row
+must agree (checked with the tolerance the other GPU tests use; bit-equal for single-token decode). Two calls in a row
 with different batches make sure stale contents of the shared array do not leak into the next call.
 
 This file sorts last on purpose: if it fails under `pytest -x`, every other test has already run.
@@ -63,7 +63,10 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
         torch.cuda.synchronize()
         err = orc.compare(ref.float().cpu().numpy(), out.float().cpu().numpy())
         assert err["max_abs"] < 1e-2 and err["mean_abs"] < 1e-3, err     # the bar of the other GPU tests
-        assert torch.equal(ref, out), err                                 # and in fact the same bits
+        if max(case["q_lens"]) == 1:
+            assert torch.equal(ref, out), err    # single-token decode takes the same code path: same bits
+        # (multi-token queries: the workspace entry point lets warps share K/V streams across m tiles, the built-in
+        #  scratch is too small for that mode's partials, so the summation order differs in the last fp32 bits)
         assert ref.abs().sum() > 0
 
 

@@ -26,6 +26,9 @@
 namespace kvq {
 namespace {
 
+#ifndef KVQ_FULL_PREFILL
+#define KVQ_FULL_PREFILL 1
+#endif
 constexpr int CHUNK = 32;      // keys per pipeline stage and per P-quantization tile
 constexpr int NWARPS = 4;
 constexpr int NTHREADS = NWARPS * 32;
@@ -250,87 +253,79 @@ struct Geom {
   static_assert(NWARPS * 16 * ACC_RS * 4 <= RING, "combine buffer aliases the ring");
 };
 
-// q fold + quantize for the 16 rows of m tile `mt` of (request, kv head); all 128 threads, 8 per row.
+// q fold + quantize for the rows of m tile `mt` of (request, kv head): one warp per row, 4 channels per lane, in
+// a rolled loop (this code runs once per item; kept small because straight-line code that is executed once
+// mostly waits on instruction fetch). The next row's q is loaded while the current one is processed.
 // The reference's implementation B does this in double (exact products q * s_k, scale = max / 127, division).
-// FP64 issue is slow enough on this part to cost microseconds per item, so the same values are carried as
-// unevaluated fp32 pairs (~2^-46); only exact rounding ties take the literal double route.
-template <int D>
+// FP64 issue is slow on this part, so the same values are carried as unevaluated fp32 pairs (~2^-46); only
+// exact rounding ties take the literal double route.
+template <int D, int NROWS>
 __device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, float* s_chi, float* s_clo, int tok,
-                                           int qlen, int kvh, int mt, int tid) {
-  constexpr int CPT = D / 8, QROW = D + 16;
-  const int row = tid >> 3, part = tid & 7, d0 = part * CPT;
-  const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-  float x[CPT];   // fp32(q * s_k): what gets quantized
-  ff amax = {0.f, 0.f};
-#pragma unroll
-  for (int e = 0; e < CPT; ++e) x[e] = 0.f;
-  float sk[CPT];   // vector loads issued up front: scalar loads inside the loop would serialize on L2 latency
-#pragma unroll
-  for (int v4 = 0; v4 < CPT / 4; ++v4) {
-    const float4 t4 = a.pc_k ? __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0) + v4)
-                             : make_float4(1.f, 1.f, 1.f, 1.f);
-    sk[4 * v4] = t4.x, sk[4 * v4 + 1] = t4.y, sk[4 * v4 + 2] = t4.z, sk[4 * v4 + 3] = t4.w;
+                                           int qlen, int kvh, int mt, int warp, int lane) {
+  constexpr int QROW = D + 16, LANES = D / 4;
+  const bool lane_on = lane < LANES;
+  const int d0 = (lane_on ? lane : 0) * 4;
+  float sk[4] = {1.f, 1.f, 1.f, 1.f};   // sk = 1 for a per-head K scale
+  if (a.pc_k) {
+    const float4 t4 = __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0));
+    sk[0] = t4.x, sk[1] = t4.y, sk[2] = t4.z, sk[3] = t4.w;
   }
-  if (rt < qlen) {
-    const __nv_bfloat16* qp = a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0;
+  auto load_row = [&](int row) {
+    const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+    uint2 raw = make_uint2(0u, 0u);
+    if (row < NROWS && rt < qlen && lane_on)
+      raw = *reinterpret_cast<const uint2*>(a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0);
+    return raw;
+  };
+  uint2 cur = load_row(warp);
+#pragma unroll 1
+  for (int row = warp; row < NROWS; row += NWARPS) {
+    const uint2 nxt = load_row(row + NWARPS);
+    float x[4] = {bf16lo(cur.x), bf16hi(cur.x), bf16lo(cur.y), bf16hi(cur.y)};
+    ff amax = {0.f, 0.f};
 #pragma unroll
-    for (int v8 = 0; v8 < CPT / 8; ++v8) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(qp + 8 * v8);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) x[8 * v8 + 2 * k] = bf16lo(w[k]), x[8 * v8 + 2 * k + 1] = bf16hi(w[k]);
-    }
-#pragma unroll
-    for (int e = 0; e < CPT; ++e) {
-      const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo (sk = 1 for a per-head K scale)
-      x[e] = p.hi;
+    for (int e = 0; e < 4; ++e) {
+      const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo
+      x[e] = p.hi;                          // fp32(q * s_k): what gets quantized
       amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
     }
-  }
 #pragma unroll
-  for (int o = 1; o < 8; o <<= 1)
-    amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
-  // sq = max(amax / 127, 1e-8)
-  ff sq;
-  {
-    const float q1 = __fdiv_rn(amax.hi, 127.f);
-    const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
-    sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
-    constexpr float E_HI = 1e-8f;
-    const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
-    if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
-  }
-  uint32_t w[CPT / 4];
-#pragma unroll
-  for (int k = 0; k < CPT / 4; ++k) {
+    for (int o = 1; o < 32; o <<= 1)
+      amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
+    // sq = max(amax / 127, 1e-8)
+    ff sq;
+    {
+      const float q1 = __fdiv_rn(amax.hi, 127.f);
+      const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
+      sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
+      constexpr float E_HI = 1e-8f;
+      const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
+      if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
+    }
     int b[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
       // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
       // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
-      const float xe = x[4 * k + e];
-      const float qf = __fdiv_rn(xe, sq.hi);
+      const float qf = __fdiv_rn(x[e], sq.hi);
       int r = __float2int_rn(qf);
       if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-3f) {
         const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
-        r = __double2int_rn(static_cast<double>(xe) / sqd);
+        r = __double2int_rn(static_cast<double>(x[e]) / sqd);
       }
       b[e] = max(-127, min(127, r));
     }
-    w[k] = pack4(b[0], b[1], b[2], b[3]);
-  }
-  if constexpr (CPT == 16)
-    *reinterpret_cast<uint4*>(&s_q[row * QROW + d0]) = make_uint4(w[0], w[1], w[2], w[3]);
-  else
-    *reinterpret_cast<uint2*>(&s_q[row * QROW + d0]) = make_uint2(w[0], w[1]);
-  if (part == 0) {
-    // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
-    ff c = sq;
-    if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
-    c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
-    s_chi[row] = c.hi;
-    s_clo[row] = c.lo;
+    if (lane_on) *reinterpret_cast<uint32_t*>(&s_q[row * QROW + d0]) = pack4(b[0], b[1], b[2], b[3]);
+    if (lane == 0) {
+      // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
+      ff c = sq;
+      if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
+      c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
+      s_chi[row] = c.hi;
+      s_clo[row] = c.lo;
+    }
+    cur = nxt;
   }
 }
 
@@ -573,14 +568,22 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           }
         }
       };
+      // A single-warp group refills a stage right after consuming it, so it can fill its whole ring now and keep
+      // HBM busy through the q prologue; a shared ring keeps one stage back for the other warps of the group.
       if (ok)
-        for (int ip = 0; ip < min(npw, NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
+        for (int ip = 0; ip < min(npw, (GS == 1 && KVQ_FULL_PREFILL) ? NSTAGE : NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
       KVQ_TL(2);
 
       // -- q prologue for every m tile of the group --
+#ifdef KVQ_EXP_NO_PROLOGUE
+      if (tid < 64) s_chi[tid] = 1e-3f, s_clo[tid] = 0.f;
+      for (int sl = 0; sl < 0; ++sl)
+#else
       for (int sl = 0; sl < GS; ++sl)
+#endif
         if (mg * GS + sl < rs.mtiles)
-          q_prologue<D>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh, mg * GS + sl, tid);
+          q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh, mg * GS + sl,
+                               warp, lane);
       __syncthreads();
       TileState<D, ROWS16> ts;
       {
@@ -611,8 +614,9 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 
       // -- main loop over the group's chunks --
       for (int i = 0; i < nig && ok; ++i) {
-        const int ipn = (i >> lgs) + NSTAGE - 1;       // keep NSTAGE - 1 of my chunks in flight
-        if ((i & (GS - 1)) == msl && ipn < npw) issue(ipn, (NSTAGE - 1) * GS);
+        const int ipn = (i >> lgs) + NSTAGE - 1;       // shared ring: keep NSTAGE - 1 of my chunks in flight
+        // (a single-warp group pre-issued NSTAGE chunks, so its first in-loop issue is chunk NSTAGE at i == 1)
+        if ((i & (GS - 1)) == msl && ipn < npw && (GS > 1 || !KVQ_FULL_PREFILL || i > 0)) issue(ipn, (NSTAGE - 1) * GS);
         const int st = cst;
         ok = ok && __all_sync(0xffffffffu, mbar_wait(gfull + st * 8, cpass & 1));
         if (!ok) break;

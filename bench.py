@@ -396,6 +396,53 @@ def run_suite(args):
                    note="KV bytes counted once although 4 m tiles (56 rows) use them; average over the copies")
 
 
+# --------------------------------------------------------------------------------------------------------
+# --workload model_step: full decode step of a Qwen2.5-7B-geometry decoder (a caller of the hot path)
+# --------------------------------------------------------------------------------------------------------
+def run_model_step(args, rank, world, local_rank):
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from kvq_b200.decode_step import DecodeStep
+
+    total_requests, ctx = args.model_requests, args.model_ctx
+    batch = total_requests // world
+    model = DecodeStep(dev, batch, ctx, seed=rank).capture()
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        model.step()
+    sync_all()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(args.steps):
+        model.step()
+    b.record()
+    sync_all()
+    ms = a.elapsed_time(b)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    if rank == 0:
+        tpot = ms / args.steps
+        print(json.dumps({
+            "workload": "model_step", "metric": "decode_tokens_per_s", "value": batch * world / (tpot * 1e-3), "unit": "tok/s",
+            "tpot_ms": tpot, "n_gpus": world, "steps": args.steps, "scaling": "strong (fixed 512 requests)" if world > 1 else "n/a",
+            "config": {"model": "Qwen2.5-7B geometry, random-init bf16 weights, vocab 152064", "requests": batch * world,
+                       "requests_per_gpu": batch, "context": ctx, "kv_cache": "int8_static paged, block 16",
+                       "parallelism": f"requests sharded over {world} GPU(s), weights replicated"},
+            "kv_bytes_per_step_per_gpu": model.kv_bytes_per_step(), "weight_bytes_per_gpu": model.weight_bytes(),
+            "data": "synthetic"}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu capture summarised in
 # profiles/decode_kernel_16x32k_ncu_full.md: 541,869,312 bytes for 16 requests x 32768 context. Traffic is
 # proportional to the requests (every CTA streams its slice of the KV bytes once), so it is scaled to the batch.
@@ -411,6 +458,10 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU (default: the headline 128)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (default: the headline 32768)")
+    ap.add_argument("--workload", default="attention", choices=["attention", "model_step"],
+                    help="model_step: full 28-layer decode step (512 requests x 6144 context over all GPUs)")
+    ap.add_argument("--model-requests", type=int, default=512)
+    ap.add_argument("--model-ctx", type=int, default=6144)
     ap.add_argument("--suite", default=None, choices=["kernels"], help="extra per-kernel lines instead of the headline")
     ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
     args = ap.parse_args()
@@ -424,6 +475,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU (there is no CPU path for the product arm)")
+    if args.workload == "model_step":
+        run_model_step(args, rank, world, local_rank)
+        return
     if args.suite == "kernels":
         run_suite(args)
         return

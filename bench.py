@@ -160,7 +160,9 @@ def run_ours(args, rank, world, local_rank):
 
     lib = ck.ext()   # raises if the native library is missing: there is no fallback path
     batch, ctx = args.batch, args.ctx
-    case = workloads.decode_batch_on_device(batch, ctx, dev, seed=1002 + rank)
+    q_len = args.q_len
+    ctx_range = (args.ctx_min, ctx) if args.ctx_min else None
+    case = workloads.decode_batch_on_device(batch, ctx, dev, seed=1002 + rank, q_len=q_len, ctx_range=ctx_range)
     q, kq, vq, st = case["q"], case["kq"], case["vq"], case["static"]
     cu, sl, bt = case["cu_seqlens_q"], case["seq_lens"], case["block_table"]
     scale = case["softmax_scale"]
@@ -168,7 +170,7 @@ def run_ours(args, rank, world, local_rank):
     bytes_per_step = kv_bytes(case["seq_lens_list"])
 
     def step():
-        ck.decode_attention(q, kq, vq, out, cu, sl, bt, scale, st, max_query_len=1)
+        ck.decode_attention(q, kq, vq, out, cu, sl, bt, scale, st, max_query_len=q_len)
 
     def sync_all():
         if world > 1:
@@ -209,7 +211,7 @@ def run_ours(args, rank, world, local_rank):
     clocks = sampler.stop() if sampler is not None else None
 
     if args.profile:   # profiling runs (ncu): kernel timings only
-        print(json.dumps({"profile_run": True, "batch": batch, "ctx": ctx, "kernel_us": [k * 1e3 for k in kernel_ms],
+        print(json.dumps({"profile_run": True, "batch": batch, "ctx": ctx, "q_len": q_len, "ctx_min": args.ctx_min, "kernel_us": [k * 1e3 for k in kernel_ms],
                           "GBps": [bytes_per_step / (k * 1e-3) / 1e9 for k in kernel_ms]}), flush=True)
         return
     # ---- end to end through the public API with host buffers ----
@@ -444,9 +446,9 @@ def run_model_step(args, rank, world, local_rank):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu capture summarised in
-# profiles/decode_kernel_16x32k_ncu_full.md: 541,869,312 bytes for 16 requests x 32768 context. Traffic is
+# profiles/decode_kernel_16x32k_ncu_full.md: 541,588,224 bytes for 16 requests x 32768 context. Traffic is
 # proportional to the requests (every CTA streams its slice of the KV bytes once), so it is scaled to the batch.
-TRAFFIC_16X32K = 537_539_584 + 4_329_728
+TRAFFIC_16X32K = 537_499_392 + 4_088_832
 
 
 def main():
@@ -463,6 +465,8 @@ def main():
     ap.add_argument("--model-requests", type=int, default=512)
     ap.add_argument("--model-ctx", type=int, default=6144)
     ap.add_argument("--suite", default=None, choices=["kernels"], help="extra per-kernel lines instead of the headline")
+    ap.add_argument("--q-len", type=int, default=1, help="query tokens per request (profile runs; headline is 1)")
+    ap.add_argument("--ctx-min", type=int, default=0, help="draw contexts uniformly from [ctx-min, ctx] (profile runs)")
     ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))

@@ -253,78 +253,93 @@ struct Geom {
   static_assert(NWARPS * 16 * ACC_RS * 4 <= RING, "combine buffer aliases the ring");
 };
 
-// q fold + quantize for the rows of m tile `mt` of (request, kv head): one warp per row, 4 channels per lane, in
-// a rolled loop (this code runs once per item; kept small because straight-line code that is executed once
-// mostly waits on instruction fetch). The next row's q is loaded while the current one is processed.
-// The reference's implementation B does this in double (exact products q * s_k, scale = max / 127, division).
-// FP64 issue is slow on this part, so the same values are carried as unevaluated fp32 pairs (~2^-46); only
-// exact rounding ties take the literal double route.
-template <int D, int NROWS>
-__device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, float* s_chi, float* s_clo, int tok,
-                                           int qlen, int kvh, int mt, int warp, int lane) {
+// One row of q (4 channels per lane): exact fold of s_k, row scale, int8 row into s_q, score scale into
+// s_chi / s_clo. Called by a full warp. The reference's implementation B does this in double (exact products
+// q * s_k, scale = max / 127, division). FP64 issue is slow on this part, so the same values are carried as
+// unevaluated fp32 pairs (~2^-46); only exact rounding ties take the literal double route.
+template <int D>
+__device__ __forceinline__ void q_quantize_row(const DecodeArgs& a, uint2 raw, const float (&sk)[4], int8_t* s_q,
+                                               float* s_chi, float* s_clo, int kvh, int row, int lane) {
   constexpr int QROW = D + 16, LANES = D / 4;
   const bool lane_on = lane < LANES;
   const int d0 = (lane_on ? lane : 0) * 4;
-  float sk[4] = {1.f, 1.f, 1.f, 1.f};   // sk = 1 for a per-head K scale
+  float x[4] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y)};
+  ff amax = {0.f, 0.f};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo
+    x[e] = p.hi;                          // fp32(q * s_k): what gets quantized
+    amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1)
+    amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
+  // sq = max(amax / 127, 1e-8)
+  ff sq;
+  {
+    const float q1 = __fdiv_rn(amax.hi, 127.f);
+    const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
+    sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
+    constexpr float E_HI = 1e-8f;
+    const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
+    if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
+  }
+  int b[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
+    // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
+    // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
+    const float qf = __fdiv_rn(x[e], sq.hi);
+    int r = __float2int_rn(qf);
+    if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-4f) {
+      const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
+      r = __double2int_rn(static_cast<double>(x[e]) / sqd);
+    }
+    b[e] = max(-127, min(127, r));
+  }
+  if (lane_on) *reinterpret_cast<uint32_t*>(&s_q[row * QROW + d0]) = pack4(b[0], b[1], b[2], b[3]);
+  if (lane == 0) {
+    // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
+    ff c = sq;
+    if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
+    c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
+    s_chi[row] = c.hi;
+    s_clo[row] = c.lo;
+  }
+}
+
+// 4 channels of row `row` of m tile `mt` for this lane (zeros for rows past the request's last query token).
+template <int D, int NROWS>
+__device__ __forceinline__ uint2 q_load_row(const DecodeArgs& a, int tok, int qlen, int kvh, int mt, int row, int lane) {
+  const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
+  uint2 raw = make_uint2(0u, 0u);
+  if (row < NROWS && rt < qlen && lane < D / 4)
+    raw = *reinterpret_cast<const uint2*>(a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + lane * 4);
+  return raw;
+}
+template <int D>
+__device__ __forceinline__ void q_load_scale(const DecodeArgs& a, int kvh, int lane, float (&sk)[4]) {
+  sk[0] = sk[1] = sk[2] = sk[3] = 1.f;   // a per-head K scale is not folded into q
   if (a.pc_k) {
-    const float4 t4 = __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + d0));
+    const float4 t4 = __ldg(reinterpret_cast<const float4*>(a.ks + kvh * D + (lane < D / 4 ? lane : 0) * 4));
     sk[0] = t4.x, sk[1] = t4.y, sk[2] = t4.z, sk[3] = t4.w;
   }
-  auto load_row = [&](int row) {
-    const int R = mt * 16 + row, rt = R / a.G, rh = R - rt * a.G;
-    uint2 raw = make_uint2(0u, 0u);
-    if (row < NROWS && rt < qlen && lane_on)
-      raw = *reinterpret_cast<const uint2*>(a.q + (tok + rt) * a.q_st + (kvh * a.G + rh) * a.q_sh + d0);
-    return raw;
-  };
-  uint2 cur = load_row(warp);
+}
+
+// q fold + quantize for the rows of m tile `mt` of (request, kv head): one warp per row in a rolled loop (this code
+// runs once per item; kept small because straight-line code that is executed once mostly waits on instruction
+// fetch). The next row's q is loaded while the current one is processed.
+template <int D, int NROWS>
+__device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, float* s_chi, float* s_clo, int tok,
+                                           int qlen, int kvh, int mt, int warp, int lane) {
+  float sk[4];
+  q_load_scale<D>(a, kvh, lane, sk);
+  uint2 cur = q_load_row<D, NROWS>(a, tok, qlen, kvh, mt, warp, lane);
 #pragma unroll 1
   for (int row = warp; row < NROWS; row += NWARPS) {
-    const uint2 nxt = load_row(row + NWARPS);
-    float x[4] = {bf16lo(cur.x), bf16hi(cur.x), bf16lo(cur.y), bf16hi(cur.y)};
-    ff amax = {0.f, 0.f};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const ff p = two_prod(x[e], sk[e]);   // exact product as hi + lo
-      x[e] = p.hi;                          // fp32(q * s_k): what gets quantized
-      amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
-    }
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1)
-      amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
-    // sq = max(amax / 127, 1e-8)
-    ff sq;
-    {
-      const float q1 = __fdiv_rn(amax.hi, 127.f);
-      const float rem = __fmaf_rn(-q1, 127.f, amax.hi);            // exact remainder of the rounded quotient
-      sq = fast_two_sum(q1, __fdiv_rn(__fadd_rn(rem, amax.lo), 127.f));
-      constexpr float E_HI = 1e-8f;
-      const float E_LO = static_cast<float>(1e-8 - static_cast<double>(E_HI));   // folded at compile time
-      if (sq.hi < E_HI || (sq.hi == E_HI && sq.lo < E_LO)) sq = ff{E_HI, E_LO};
-    }
-    int b[4];
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      // rint(x / sq): the fp32 quotient is within 2e-5 of the exact one (|quotient| <= 127). Only a value that
-      // close to k + 0.5 takes the reference's literal double-precision route (exact ties do occur with a
-      // per-head K scale, where x / sq is a ratio of bf16 numbers, and there the double roundings decide).
-      const float qf = __fdiv_rn(x[e], sq.hi);
-      int r = __float2int_rn(qf);
-      if (fabsf(fabsf(qf - static_cast<float>(r)) - 0.5f) < 1e-3f) {
-        const double sqd = fmax((static_cast<double>(amax.hi) + static_cast<double>(amax.lo)) / 127.0, 1e-8);
-        r = __double2int_rn(static_cast<double>(x[e]) / sqd);
-      }
-      b[e] = max(-127, min(127, r));
-    }
-    if (lane_on) *reinterpret_cast<uint32_t*>(&s_q[row * QROW + d0]) = pack4(b[0], b[1], b[2], b[3]);
-    if (lane == 0) {
-      // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
-      ff c = sq;
-      if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
-      c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
-      s_chi[row] = c.hi;
-      s_clo[row] = c.lo;
-    }
+    const uint2 nxt = q_load_row<D, NROWS>(a, tok, qlen, kvh, mt, row + NWARPS, lane);
+    q_quantize_row<D>(a, cur, sk, s_q, s_chi, s_clo, kvh, row, lane);
     cur = nxt;
   }
 }
@@ -474,7 +489,13 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int krow = lane & 7, kmat = lane >> 3;
   const int vrow = (lane & 1) + 8 * ((lane >> 1) & 1) + 2 * ((lane >> 2) & 3) + 16 * (lane >> 4);
 
-  int cur_gs = 0;      // group size the barriers are currently initialised for (0: not yet)
+  // Barriers start out partitioned for single-warp groups (decode); re-partitioned below if a request needs more.
+  if (tid == 0) {
+    for (int i = 0; i < NSTG; ++i) mbar_init(smem_u32(&s_full[i]), 1), mbar_init(smem_u32(&s_empty[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fence_proxy_async();   // ordered before the first TMA issue by the __syncthreads of the request search below
+  int cur_gs = 1;      // group size the barriers are currently initialised for
   int cst = 0, cpass = 0;  // consumer position of this warp's group in its ring: stage, completed passes
   bool ok = true;
   int u = ubeg;
@@ -500,7 +521,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     if (GS != cur_gs) {
       if (tid == 0) {
         for (int i = 0; i < NSTG; ++i) {
-          if (cur_gs != 0) mbar_inval(smem_u32(&s_full[i])), mbar_inval(smem_u32(&s_empty[i]));
+          mbar_inval(smem_u32(&s_full[i])), mbar_inval(smem_u32(&s_empty[i]));
           mbar_init(smem_u32(&s_full[i]), 1);
           mbar_init(smem_u32(&s_empty[i]), GS);
         }
@@ -568,6 +589,16 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           }
         }
       };
+      // Single-token decode: this warp's q rows are requested before the K/V prefetch below. Behind a full ring of
+      // bulk loads (~200 KB per SM) a plain load waits for microseconds; ahead of it, it costs one round trip.
+      uint2 q_early[NROWS / NWARPS];
+      float sk_early[4];
+      if constexpr (!ROWS16) {
+        q_load_scale<D>(a, kvh, lane, sk_early);
+#pragma unroll
+        for (int k = 0; k < NROWS / NWARPS; ++k)
+          q_early[k] = q_load_row<D, NROWS>(a, tok, qlen, kvh, mg, warp + NWARPS * k, lane);
+      }
       // A single-warp group refills a stage right after consuming it, so it can fill its whole ring now and keep
       // HBM busy through the q prologue; a shared ring keeps one stage back for the other warps of the group.
       if (ok)
@@ -575,15 +606,16 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       KVQ_TL(2);
 
       // -- q prologue for every m tile of the group --
-#ifdef KVQ_EXP_NO_PROLOGUE
-      if (tid < 64) s_chi[tid] = 1e-3f, s_clo[tid] = 0.f;
-      for (int sl = 0; sl < 0; ++sl)
-#else
-      for (int sl = 0; sl < GS; ++sl)
-#endif
-        if (mg * GS + sl < rs.mtiles)
-          q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh, mg * GS + sl,
-                               warp, lane);
+      if constexpr (!ROWS16) {
+#pragma unroll
+        for (int k = 0; k < NROWS / NWARPS; ++k)
+          q_quantize_row<D>(a, q_early[k], sk_early, s_q, s_chi, s_clo, kvh, warp + NWARPS * k, lane);
+      } else {
+        for (int sl = 0; sl < GS; ++sl)
+          if (mg * GS + sl < rs.mtiles)
+            q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh,
+                                 mg * GS + sl, warp, lane);
+      }
       __syncthreads();
       TileState<D, ROWS16> ts;
       {

@@ -1,6 +1,8 @@
 // Elementwise kernels of the static INT8 KV-cache path: fused quantize + paged cache write, standalone q
-// quantization, page dequantization. All three are pure HBM streaming work: one thread moves 16 channels
-// with 16-byte loads and 16-byte stores, and the grid is flat over (row, 16-channel group) items.
+// quantization, page dequantization. All three are pure HBM streaming work. The write and dequantize kernels
+// move 8 channels per item, so that both sides are fully coalesced: 16-byte loads of bf16 / 8-byte stores of
+// int8 when quantizing, 8-byte loads / 16-byte stores when dequantizing (consecutive lanes touch consecutive
+// bytes in every instruction); each thread has several items in flight.
 #include "kvq_common.cuh"
 
 namespace kvq {
@@ -8,23 +10,28 @@ namespace {
 
 constexpr int kThreads = 256;
 
-__device__ __forceinline__ void load16f(const float* p, float (&x)[16]) {
+// 8 scale values for channels d0..d0+7 of head h: per channel from [H, D], or the head's single value.
+__device__ __forceinline__ void load_scale8(const float* base, int per_channel, int h, int D, int d0, float (&s)[8]) {
+  if (per_channel) {
+    const float4 lo = __ldg(reinterpret_cast<const float4*>(base + h * D + d0));
+    const float4 hi = __ldg(reinterpret_cast<const float4*>(base + h * D + d0) + 1);
+    s[0] = lo.x, s[1] = lo.y, s[2] = lo.z, s[3] = lo.w, s[4] = hi.x, s[5] = hi.y, s[6] = hi.z, s[7] = hi.w;
+  } else {
+    const float one = __ldg(base + h);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
-    x[4 * i] = v.x, x[4 * i + 1] = v.y, x[4 * i + 2] = v.z, x[4 * i + 3] = v.w;
+    for (int e = 0; e < 8; ++e) s[e] = one;
   }
 }
 
-__device__ __forceinline__ void load16bf(const __nv_bfloat16* p, float (&x)[16]) {
-  const uint4 a = ld_stream16(p), b = ld_stream16(p + 8);
-  const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) x[2 * i] = bf16lo(w[i]), x[2 * i + 1] = bf16hi(w[i]);
+__device__ __forceinline__ uint2 ld_stream8(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
 }
 
 // ------------------------------------------------------------------------------------------------------
-// Fused quantize + cache write. Item = (token, kv head, 16-channel group).
+// Fused quantize + cache write. Item = (token, kv head, 8-channel group); kItems items per thread, one block of
+// kThreads * kItems consecutive items per CTA, every load issued before the first use.
 // ------------------------------------------------------------------------------------------------------
 struct QuantCacheArgs {
   const __nv_bfloat16 *key, *value;
@@ -32,127 +39,129 @@ struct QuantCacheArgs {
   const int64_t* slots;
   const float *ks, *vs, *kmu;
   int64_t n_items;
-  int H, D, groups;  // groups = D / 16
+  int H, D, groups;  // groups = D / 8
   int block_size, bs_shift;  // bs_shift >= 0 when block_size is a power of two
   int64_t k_st, k_sh, v_st, v_sh, kc_sb, kc_sn, kc_sh, vc_sb, vc_sn, vc_sh;
   int pc_k, pc_v;
 };
 
-__global__ void __launch_bounds__(kThreads) quant_cache_kernel(const QuantCacheArgs a) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (i >= a.n_items) return;
-  const int per_tok = a.H * a.groups;
-  const int64_t tok = i / per_tok;
-  const int rem = static_cast<int>(i - tok * per_tok);
-  const int h = rem / a.groups, d0 = (rem - h * a.groups) * 16;
-  // every load below is independent of the slot: issue them all before looking at it (one DRAM round trip)
-  float k[16], v[16], sk[16], sv[16], mu[16];
-  load16bf(a.key + tok * a.k_st + h * a.k_sh + d0, k);
-  load16bf(a.value + tok * a.v_st + h * a.v_sh + d0, v);
-  const int64_t slot = __ldg(a.slots + tok);
-  load16f(a.kmu + h * a.D + d0, mu);
-  if (a.pc_k) {
-    load16f(a.ks + h * a.D + d0, sk);
-  } else {
-    const float s = __ldg(a.ks + h);
+constexpr int kItems = 2;
+
+__device__ __forceinline__ uint2 quant8(uint4 raw, const float (&mu)[8], const float (&sc)[8], bool centre) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  int q[8];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) sk[e] = s;
-  }
-  if (a.pc_v) {
-    load16f(a.vs + h * a.D + d0, sv);
-  } else {
-    const float s = __ldg(a.vs + h);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) sv[e] = s;
-  }
-  if (slot < 0) return;  // padding token
-  int64_t blk, off;
-  if (a.bs_shift >= 0) {
-    blk = slot >> a.bs_shift, off = slot & (a.block_size - 1);
-  } else {
-    blk = slot / a.block_size, off = slot - blk * a.block_size;
-  }
-  uint32_t kw[4], vw[4];
-#pragma unroll
-  for (int w = 0; w < 4; ++w) {
+  for (int k = 0; k < 4; ++k) {
     // fp32 subtract, IEEE divide, round half to even, clamp: the order the torch quantizer uses
-    kw[w] = pack4(quant1(__fsub_rn(k[4 * w], mu[4 * w]), sk[4 * w]), quant1(__fsub_rn(k[4 * w + 1], mu[4 * w + 1]), sk[4 * w + 1]),
-                  quant1(__fsub_rn(k[4 * w + 2], mu[4 * w + 2]), sk[4 * w + 2]),
-                  quant1(__fsub_rn(k[4 * w + 3], mu[4 * w + 3]), sk[4 * w + 3]));
-    vw[w] = pack4(quant1(v[4 * w], sv[4 * w]), quant1(v[4 * w + 1], sv[4 * w + 1]), quant1(v[4 * w + 2], sv[4 * w + 2]),
-                  quant1(v[4 * w + 3], sv[4 * w + 3]));
+    const float lo = bf16lo(w[k]), hi = bf16hi(w[k]);
+    q[2 * k] = quant1(centre ? __fsub_rn(lo, mu[2 * k]) : lo, sc[2 * k]);
+    q[2 * k + 1] = quant1(centre ? __fsub_rn(hi, mu[2 * k + 1]) : hi, sc[2 * k + 1]);
   }
-  *reinterpret_cast<uint4*>(a.kc + blk * a.kc_sb + off * a.kc_sn + h * a.kc_sh + d0) = make_uint4(kw[0], kw[1], kw[2], kw[3]);
-  *reinterpret_cast<uint4*>(a.vc + blk * a.vc_sb + off * a.vc_sn + h * a.vc_sh + d0) = make_uint4(vw[0], vw[1], vw[2], vw[3]);
+  return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+}
+
+__global__ void __launch_bounds__(kThreads) quant_cache_kernel(const QuantCacheArgs a) {
+  const int per_tok = a.H * a.groups;
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * (kThreads * kItems) + threadIdx.x;
+  uint4 kr[kItems], vr[kItems];
+  int64_t slot[kItems];
+  int hh[kItems], dd[kItems];
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const int64_t i = base + u * kThreads;
+    slot[u] = -1;
+    if (i < a.n_items) {
+      const int64_t tok = i / per_tok;
+      const int rem = static_cast<int>(i - tok * per_tok);
+      hh[u] = rem / a.groups, dd[u] = (rem - hh[u] * a.groups) * 8;
+      kr[u] = ld_stream16(a.key + tok * a.k_st + hh[u] * a.k_sh + dd[u]);
+      vr[u] = ld_stream16(a.value + tok * a.v_st + hh[u] * a.v_sh + dd[u]);
+      slot[u] = __ldg(a.slots + tok);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    if (slot[u] < 0) continue;  // padding token (or past the end)
+    int64_t blk, off;
+    if (a.bs_shift >= 0) {
+      blk = slot[u] >> a.bs_shift, off = slot[u] & (a.block_size - 1);
+    } else {
+      blk = slot[u] / a.block_size, off = slot[u] - blk * a.block_size;
+    }
+    float sk[8], sv[8], mu[8];
+    load_scale8(a.kmu, 1, hh[u], a.D, dd[u], mu);
+    load_scale8(a.ks, a.pc_k, hh[u], a.D, dd[u], sk);
+    load_scale8(a.vs, a.pc_v, hh[u], a.D, dd[u], sv);
+    *reinterpret_cast<uint2*>(a.kc + blk * a.kc_sb + off * a.kc_sn + hh[u] * a.kc_sh + dd[u]) = quant8(kr[u], mu, sk, true);
+    *reinterpret_cast<uint2*>(a.vc + blk * a.vc_sb + off * a.vc_sn + hh[u] * a.vc_sh + dd[u]) = quant8(vr[u], mu, sv, false);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------
-// q fold + quantize. 8 lanes per (token, q head) row of 128 channels, 16 channels per lane.
+// q fold + quantize. 16 lanes per (token, q head) row of 128 channels, 8 channels per lane: one 16-byte load,
+// one 8-byte store, abs-max over the 16 (group 128) or 4 (group 32) lanes of a group by shuffles.
 // ------------------------------------------------------------------------------------------------------
 template <int GROUP>
 __global__ void __launch_bounds__(kThreads) quant_q_kernel(const __nv_bfloat16* __restrict__ q, const float* __restrict__ ks,
                                                            int8_t* __restrict__ q_i8, float* __restrict__ q_scale,
                                                            int64_t n_rows, int Hq, int G, int64_t q_st, int64_t q_sh,
                                                            int pc_k) {
-  constexpr int D = 128, LPR = D / 16;
+  constexpr int D = 128, LPR = D / 8;
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const int part = static_cast<int>(i % LPR);
   const int64_t row = i / LPR;
   const bool live = row < n_rows;
   const int64_t r = live ? row : n_rows - 1;  // idle lanes of the last warp still take part in the shuffles
   const int64_t t = r / Hq;
-  const int h = static_cast<int>(r - t * Hq), d0 = part * 16;
-  float x[16];
-  load16bf(q + t * q_st + h * q_sh + d0, x);
-  if (pc_k) {
-    float s[16];
-    load16f(ks + (h / G) * D + d0, s);
+  const int h = static_cast<int>(r - t * Hq), d0 = part * 8;
+  const uint4 raw = ld_stream16(q + t * q_st + h * q_sh + d0);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  float x[8];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) x[e] = __fmul_rn(x[e], s[e]);
+  for (int k = 0; k < 4; ++k) x[2 * k] = bf16lo(w[k]), x[2 * k + 1] = bf16hi(w[k]);
+  if (pc_k) {   // a per-head K scale is not folded into q and k_scale is not read
+    float s8[8];
+    load_scale8(ks, 1, h / G, D, d0, s8);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = __fmul_rn(x[e], s8[e]);
   }
   float amax = 0.f;
 #pragma unroll
-  for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(x[e]));
+  for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[e]));
 #pragma unroll
-  for (int o = 1; o < GROUP / 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  for (int o = 1; o < GROUP / 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
   const float s = fmaxf(__fdiv_rn(amax, 127.f), 1e-8f);
   if (!live) return;
-  uint32_t w[4];
-#pragma unroll
-  for (int k = 0; k < 4; ++k)
-    w[k] = pack4(quant1(x[4 * k], s), quant1(x[4 * k + 1], s), quant1(x[4 * k + 2], s), quant1(x[4 * k + 3], s));
-  *reinterpret_cast<uint4*>(q_i8 + row * D + d0) = make_uint4(w[0], w[1], w[2], w[3]);
-  if (part % (GROUP / 16) == 0) q_scale[row * (D / GROUP) + d0 / GROUP] = s;
+  *reinterpret_cast<uint2*>(q_i8 + row * D + d0) =
+      make_uint2(pack4(quant1(x[0], s), quant1(x[1], s), quant1(x[2], s), quant1(x[3], s)),
+                 pack4(quant1(x[4], s), quant1(x[5], s), quant1(x[6], s), quant1(x[7], s)));
+  if (part % (GROUP / 8) == 0) q_scale[row * (D / GROUP) + d0 / GROUP] = s;
 }
 
 // ------------------------------------------------------------------------------------------------------
-// Page dequantization. Item = (output page, slot, kv head, 16-channel group); the output is contiguous
-// [pages, block, H, D], so item i of page p writes 32 bytes at element offset 16 * (p * items_per_page + i).
+// Page dequantization. Item = (output page, slot, kv head, 8-channel group); the output is contiguous
+// [pages, block, H, D], so item i of page p writes 16 bytes at element offset 8 * (p * items_per_page + i).
+// One CTA per output page: the source page id is looked up once, then every thread issues all of its 8-byte
+// loads (kDqItems items of K and of V) before converting any of them.
 // ------------------------------------------------------------------------------------------------------
 struct DequantArgs {
   const int8_t *kc, *vc;
   __nv_bfloat16 *ko, *vo;
   const int32_t *block_table, *src_req, *src_j;
   const float *ks, *vs;
-  int64_t n_items, bt_stride;
-  int H, D, groups, block_size;
+  int64_t bt_stride;
+  int H, D, groups, block_size;   // groups = D / 8
   int64_t kc_sb, kc_sn, kc_sh, vc_sb, vc_sn, vc_sh;
   int pc_k, pc_v;
 };
 
-__device__ __forceinline__ void dequant_store(uint4 raw, __nv_bfloat16* dst, const float* scale, int per_channel) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-  float s[16];
-  if (per_channel) {
-    load16f(scale, s);
-  } else {
-    const float one = __ldg(scale);
+constexpr int kDqItems = 4;
+
+__device__ __forceinline__ uint4 dequant8(uint2 raw, const float (&s)[8]) {
+  const uint32_t w[2] = {raw.x, raw.y};
+  uint32_t o[4];
 #pragma unroll
-    for (int e = 0; e < 16; ++e) s[e] = one;
-  }
-  uint32_t o[8];
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
+  for (int k = 0; k < 2; ++k) {
     // int8 -> fp32 (exact), fp32 multiply, round to nearest even bf16
     const float f0 = static_cast<float>(static_cast<int8_t>(w[k] & 0xff));
     const float f1 = static_cast<float>(static_cast<int8_t>((w[k] >> 8) & 0xff));
@@ -161,13 +170,8 @@ __device__ __forceinline__ void dequant_store(uint4 raw, __nv_bfloat16* dst, con
     o[2 * k] = pack_bf16x2(__fmul_rn(f0, s[4 * k]), __fmul_rn(f1, s[4 * k + 1]));
     o[2 * k + 1] = pack_bf16x2(__fmul_rn(f2, s[4 * k + 2]), __fmul_rn(f3, s[4 * k + 3]));
   }
-  reinterpret_cast<uint4*>(dst)[0] = make_uint4(o[0], o[1], o[2], o[3]);
-  reinterpret_cast<uint4*>(dst)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+  return make_uint4(o[0], o[1], o[2], o[3]);
 }
-
-// One CTA per output page: the source page id is looked up once, then every thread issues all of its 16-byte
-// loads (kUnroll items of K and of V) before converting any of them.
-constexpr int kUnroll = 2;
 
 __global__ void __launch_bounds__(kThreads) dequant_pages_kernel(const DequantArgs a) {
   const int64_t p = blockIdx.x;
@@ -175,26 +179,29 @@ __global__ void __launch_bounds__(kThreads) dequant_pages_kernel(const DequantAr
   const int64_t src = __ldg(a.block_table + static_cast<int64_t>(__ldg(a.src_req + p)) * a.bt_stride + __ldg(a.src_j + p));
   const int8_t* kp = a.kc + src * a.kc_sb;
   const int8_t* vp = a.vc + src * a.vc_sb;
-  for (int base = threadIdx.x; base < per_page; base += kThreads * kUnroll) {
-    uint4 kr[kUnroll], vr[kUnroll];
-    int hh[kUnroll], dd[kUnroll];
+  for (int base = threadIdx.x; base < per_page; base += kThreads * kDqItems) {
+    uint2 kr[kDqItems], vr[kDqItems];
+    int hh[kDqItems], dd[kDqItems];
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kDqItems; ++u) {
       const int i = base + u * kThreads;
       const int n = i / per_slot, rem = i - n * per_slot;
-      hh[u] = rem / a.groups, dd[u] = (rem - hh[u] * a.groups) * 16;
+      hh[u] = rem / a.groups, dd[u] = (rem - hh[u] * a.groups) * 8;
       if (i < per_page) {
-        kr[u] = ld_stream16(kp + n * a.kc_sn + hh[u] * a.kc_sh + dd[u]);
-        vr[u] = ld_stream16(vp + n * a.vc_sn + hh[u] * a.vc_sh + dd[u]);
+        kr[u] = ld_stream8(kp + n * a.kc_sn + hh[u] * a.kc_sh + dd[u]);
+        vr[u] = ld_stream8(vp + n * a.vc_sn + hh[u] * a.vc_sh + dd[u]);
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
+    for (int u = 0; u < kDqItems; ++u) {
       const int i = base + u * kThreads;
       if (i >= per_page) continue;
-      const int64_t o = (p * per_page + i) * 16;
-      dequant_store(kr[u], a.ko + o, a.pc_k ? a.ks + hh[u] * a.D + dd[u] : a.ks + hh[u], a.pc_k);
-      dequant_store(vr[u], a.vo + o, a.pc_v ? a.vs + hh[u] * a.D + dd[u] : a.vs + hh[u], a.pc_v);
+      const int64_t o = (p * per_page + i) * 8;
+      float sk[8], sv[8];
+      load_scale8(a.ks, a.pc_k, hh[u], a.D, dd[u], sk);
+      load_scale8(a.vs, a.pc_v, hh[u], a.D, dd[u], sv);
+      *reinterpret_cast<uint4*>(a.ko + o) = dequant8(kr[u], sk);
+      *reinterpret_cast<uint4*>(a.vo + o) = dequant8(vr[u], sv);
     }
   }
 }
@@ -233,14 +240,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_quant_cache(const void
   a.key = static_cast<const __nv_bfloat16*>(key), a.value = static_cast<const __nv_bfloat16*>(value);
   a.kc = static_cast<int8_t*>(k_cache), a.vc = static_cast<int8_t*>(v_cache);
   a.slots = slots, a.ks = k_scale, a.vs = v_scale, a.kmu = k_mu;
-  a.H = num_kv_heads, a.D = head_dim, a.groups = head_dim / 16;
+  a.H = num_kv_heads, a.D = head_dim, a.groups = head_dim / 8;
   a.n_items = num_tokens * num_kv_heads * a.groups;
   a.block_size = block_size, a.bs_shift = ilog2_exact(block_size);
   a.k_st = key_stride_t, a.k_sh = key_stride_h, a.v_st = value_stride_t, a.v_sh = value_stride_h;
   a.kc_sb = kc_stride_b, a.kc_sn = kc_stride_n, a.kc_sh = kc_stride_h;
   a.vc_sb = vc_stride_b, a.vc_sn = vc_stride_n, a.vc_sh = vc_stride_h;
   a.pc_k = k_per_channel, a.pc_v = v_per_channel;
-  const int64_t blocks = (a.n_items + kThreads - 1) / kThreads;
+  const int64_t blocks = (a.n_items + kThreads * kItems - 1) / (kThreads * kItems);
   quant_cache_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
@@ -257,7 +264,7 @@ extern "C" __attribute__((visibility("default"))) int kvq_quant_q(const void* q,
                   (!k_per_channel || aligned16(k_scale)),
               "quant_q: rows must be 16-byte aligned");
   const int64_t rows = num_tokens * num_q_heads;
-  const int64_t blocks = (rows * 8 + kThreads - 1) / kThreads;
+  const int64_t blocks = (rows * 16 + kThreads - 1) / kThreads;
   auto s = reinterpret_cast<cudaStream_t>(stream);
   const auto* qp = static_cast<const __nv_bfloat16*>(q);
   auto* qi = static_cast<int8_t*>(q_i8);
@@ -291,8 +298,7 @@ extern "C" __attribute__((visibility("default"))) int kvq_dequant_pages(const vo
   a.kc = static_cast<const int8_t*>(k_cache), a.vc = static_cast<const int8_t*>(v_cache);
   a.ko = static_cast<__nv_bfloat16*>(k_out), a.vo = static_cast<__nv_bfloat16*>(v_out);
   a.block_table = block_table, a.src_req = src_req, a.src_j = src_j, a.ks = k_scale, a.vs = v_scale;
-  a.H = num_kv_heads, a.D = head_dim, a.groups = head_dim / 16, a.block_size = block_size;
-  a.n_items = num_pages * block_size * num_kv_heads * a.groups;
+  a.H = num_kv_heads, a.D = head_dim, a.groups = head_dim / 8, a.block_size = block_size;
   a.bt_stride = bt_stride;
   a.kc_sb = kc_stride_b, a.kc_sn = kc_stride_n, a.kc_sh = kc_stride_h;
   a.vc_sb = vc_stride_b, a.vc_sn = vc_stride_n, a.vc_sh = vc_stride_h;

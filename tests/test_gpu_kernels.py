@@ -272,3 +272,42 @@ def test_check_inputs_reports_bad_pages():
     with pytest.raises(RuntimeError, match="kvq input check"):
         ck.check_inputs(case["q"].to(DEV), case["kq"].to(DEV), case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV),
                         bt.to(DEV), None)
+
+
+def test_strided_q_and_out_rows():
+    """q as a slice of a fused qkv activation and out as a slice of a wider buffer (token / head strides)."""
+    case = workloads.paged_case(51, 28, 4, 128, [1, 4, 1, 8], [200, 513, 31, 1000], q_std=2.0)
+    ref = oracle_attention(case)
+    T = case["q"].shape[0]
+    qkv = torch.zeros(T, 28 + 8, 128, dtype=torch.bfloat16, device=DEV)
+    qkv[:, :28] = case["q"].to(DEV)
+    wide = torch.full((T, 28, 256), 7.0, dtype=torch.bfloat16, device=DEV)
+    out = wide[:, :, :128]
+    ck.decode_attention(qkv[:, :28], case["kq"].to(DEV), case["vq"].to(DEV), out, case["cu_seqlens_q"].to(DEV),
+                        case["seq_lens"].to(DEV), case["block_table"].to(DEV), case["softmax_scale"], to_dev(case["static"]),
+                        max_query_len=8)
+    torch.cuda.synchronize()
+    assert ck.decode_status() == 0
+    assert_close(ref, out.float().cpu().numpy(), "strided")
+    assert (wide[:, :, 128:] == 7.0).all()          # nothing written outside the rows
+
+
+def test_garbage_table_entries_past_the_context_are_harmless():
+    """Entries of the block table beyond a request's pages may hold anything (vLLM leaves stale ids there): they are
+    either never read or land in masked keys; out-of-range ids make TMA zero-fill instead of faulting."""
+    case = workloads.paged_case(52, 28, 4, 128, [1, 1, 3], [100, 16, 530])
+    ref = oracle_attention(case)
+    bt = case["block_table"].clone()
+    for r, L in enumerate(case["seq_lens"].tolist()):
+        pages = (L + 15) // 16
+        bt[r, pages:] = torch.tensor([-1, 2 ** 30, 12345678][r % 3], dtype=torch.int32)
+    case["block_table"] = bt
+    assert_close(ref, run_decode(case), "garbage table")
+
+
+def test_all_requests_skipped_leaves_output_alone():
+    """A batch with only padding (q_len 0) and long (q_len > 8) requests: the call is a no-op on `out`."""
+    case = workloads.paged_case(53, 28, 4, 128, [0, 12, 0], [40, 300, 9])
+    out = torch.full_like(case["q"], 7.0).to(DEV)
+    got = run_decode(case, out=out, max_query_len=12)
+    assert (got == 7.0).all()

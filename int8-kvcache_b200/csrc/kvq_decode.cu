@@ -919,7 +919,7 @@ int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t 
   e.key = key;
   const CUresult r = g_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), gdim, gstr, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              D == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_64B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (cache strides %lld/%lld/%lld)", static_cast<int>(r),
               static_cast<long long>(sb), static_cast<long long>(sn), static_cast<long long>(sh));

@@ -109,12 +109,13 @@ def config1(seed=1001):
 
 
 def decode_batch_on_device(batch, ctx, device, seed=1002, q_len=1, ctx_range=None, hq=HQ, hkv=HKV, d=D,
-                           block_size=BLOCK, chunk_blocks=16384):
+                           block_size=BLOCK, chunk_blocks=16384, head_major=False):
     """Large decode / short-query batch built directly on `device` (the pool is several GB).
 
     K/V pools are generated and quantized chunk by chunk with per-chunk seeds; the static scales use the
     analytic bound 4.5 sigma_c / 127 instead of a data pass, so no bf16 copy of the pool is ever held.
     ctx_range=(lo, hi) draws per-request contexts uniformly from [lo, hi]; otherwise all are `ctx`.
+    head_major=True stores each (page, head) tile contiguously (2 KB for 16 x 128 int8) instead of token-major.
     Returns the same keys as paged_case minus the bf16 pools."""
     gen = torch.Generator(device="cpu").manual_seed(seed)
     if ctx_range is not None:
@@ -135,8 +136,12 @@ def decode_batch_on_device(batch, ctx, device, seed=1002, q_len=1, ctx_range=Non
     vsig = channel_sigmas(gen, hkv, d, 0.5, 2.0)
     static = {"k_scale": (4.5 * ksig / QMAX).contiguous(), "v_scale": (4.5 * vsig / QMAX).contiguous(),
               "k_mu": torch.zeros(hkv, d)}
-    kq = torch.empty(num_blocks, block_size, hkv, d, dtype=torch.int8, device=device)
-    vq = torch.empty_like(kq)
+    if head_major:   # pages stored [block, head, slot, channel]; the kernels see the usual [block, slot, head, channel] view
+        kq = torch.empty(num_blocks, hkv, block_size, d, dtype=torch.int8, device=device).transpose(1, 2)
+        vq = torch.empty(num_blocks, hkv, block_size, d, dtype=torch.int8, device=device).transpose(1, 2)
+    else:
+        kq = torch.empty(num_blocks, block_size, hkv, d, dtype=torch.int8, device=device)
+        vq = torch.empty_like(kq)
     dgen = torch.Generator(device=device)
     ks_d, vs_d = static["k_scale"].to(device), static["v_scale"].to(device)
     ksig_d, vsig_d = ksig.to(device), vsig.to(device)

@@ -311,3 +311,30 @@ def test_all_requests_skipped_leaves_output_alone():
     out = torch.full_like(case["q"], 7.0).to(DEV)
     got = run_decode(case, out=out, max_query_len=12)
     assert (got == 7.0).all()
+
+
+def test_head_major_pages():
+    """Caches stored [block, head, slot, channel] (each (page, head) tile contiguous) and passed as the usual
+    [block, slot, head, channel] views: slot stride < head stride, so the tensor maps order their dims differently."""
+    case = workloads.paged_case(54, 32, 8, 128, [1, 1, 6, 1], [700, 90, 333, 2049])
+    ref = oracle_attention(case)
+    q = case["q"].to(DEV)
+    kq = case["kq"].to(DEV).permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    vq = case["vq"].to(DEV).permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    assert kq.stride(1) == 128 and kq.stride(2) == 16 * 128
+    out = torch.zeros_like(q)
+    ck.decode_attention(q, kq, vq, out, case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV),
+                        case["block_table"].to(DEV), case["softmax_scale"], to_dev(case["static"]), max_query_len=6)
+    torch.cuda.synchronize()
+    assert ck.decode_status() == 0
+    assert_close(ref, out.float().cpu().numpy(), "head-major")
+    # the write kernel into the same layout
+    w = workloads.write_case(55, 100, 8, 128, num_blocks=16)
+    kc = torch.zeros(16, 8, 16, 128, dtype=torch.int8, device=DEV).transpose(1, 2)
+    vc = torch.zeros(16, 8, 16, 128, dtype=torch.int8, device=DEV).transpose(1, 2)
+    ck.quant_reshape_and_cache(w["key"].to(DEV), w["value"].to(DEV), kc, vc, w["slots"].to(DEV), to_dev(w["static"]))
+    rk, rv = np.zeros((16, 16, 8, 128), np.int8), np.zeros((16, 16, 8, 128), np.int8)
+    st = w["static"]
+    orc.quant_cache_write(w["key"].float().numpy(), w["value"].float().numpy(), rk, rv, w["slots"].numpy(),
+                          st["k_scale"].numpy(), st["v_scale"].numpy(), st["k_mu"].numpy())
+    assert np.array_equal(kc.cpu().numpy(), rk) and np.array_equal(vc.cpu().numpy(), rv)

@@ -4,15 +4,16 @@
 //   plan_kernel     one block: per-request work in 32-key units, exclusive prefix sum, units per CTA
 //   decode_kernel   one CTA per slice of the global unit range (the range is cut evenly over
 //                   #SMs x resident CTAs, so every CTA streams the same number of KV bytes whatever the
-//                   mix of context lengths); a slice covers whole (request, kv head, m tile) items and at
+//                   mix of context lengths); a slice covers whole (request, kv head, m-tile group) items and at
 //                   most two partial ones, whose (acc, max, sum) go to the workspace
 //   merge_kernel    items that were cut across CTAs: combine their partials into the output
 //
-// Inside decode_kernel each warp owns a ring of NSTAGE stages fed by TMA (cp.async.bulk.tensor, 128-byte
-// swizzle, one 16-key x head_dim box per page half, completion on an mbarrier) and works on its own
-// 32-key chunks: S = Q.K^T with mma.sync m16n8k32 s8 (K fragments by ldmatrix), fp32 online softmax in the
-// exp2 domain, P quantized to int8 per (row, chunk), O += P.V with the same mma (V fragments by the 8-bit
-// transposing ldmatrix of sm_100), then the warps of the CTA are combined through shared memory.
+// Inside decode_kernel the four warps of a CTA form groups of 1, 2 or 4 (per request, by its number of 16-row
+// m tiles). A group owns a slice of the TMA ring (cp.async.bulk.tensor, 128-byte swizzle, one 16-key x head_dim
+// box per page half, full/empty mbarriers) and streams its own 32-key chunks; every warp of the group reads
+// the same stage and works on its own m tile: S = Q.K^T with mma.sync m16n8k32 s8 (K fragments by ldmatrix),
+// fp32 online softmax, P quantized to int8 per (row, chunk), O += P.V with the same mma (V fragments by the
+// 8-bit transposing ldmatrix of sm_100). Warps that worked on the same m tile are combined through shared memory.
 //
 // Numerics follow "implementation B" of the reference (kvq/int8_ref.py:108-143, kernel restatement
 // kvq/cuda/int8_kv.cu:11-15): see include/kvq_b200.h.
@@ -26,9 +27,6 @@
 namespace kvq {
 namespace {
 
-#ifndef KVQ_FULL_PREFILL
-#define KVQ_FULL_PREFILL 1
-#endif
 constexpr int CHUNK = 32;      // keys per pipeline stage and per P-quantization tile
 constexpr int NWARPS = 4;
 constexpr int NTHREADS = NWARPS * 32;
@@ -602,7 +600,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       // A single-warp group refills a stage right after consuming it, so it can fill its whole ring now and keep
       // HBM busy through the q prologue; a shared ring keeps one stage back for the other warps of the group.
       if (ok)
-        for (int ip = 0; ip < min(npw, (GS == 1 && KVQ_FULL_PREFILL) ? NSTAGE : NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
+        for (int ip = 0; ip < min(npw, GS == 1 ? NSTAGE : NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
       KVQ_TL(2);
 
       // -- q prologue for every m tile of the group --
@@ -648,7 +646,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       for (int i = 0; i < nig && ok; ++i) {
         const int ipn = (i >> lgs) + NSTAGE - 1;       // shared ring: keep NSTAGE - 1 of my chunks in flight
         // (a single-warp group pre-issued NSTAGE chunks, so its first in-loop issue is chunk NSTAGE at i == 1)
-        if ((i & (GS - 1)) == msl && ipn < npw && (GS > 1 || !KVQ_FULL_PREFILL || i > 0)) issue(ipn, (NSTAGE - 1) * GS);
+        if ((i & (GS - 1)) == msl && ipn < npw && (GS > 1 || i > 0)) issue(ipn, (NSTAGE - 1) * GS);
         const int st = cst;
         ok = ok && __all_sync(0xffffffffu, mbar_wait(gfull + st * 8, cpass & 1));
         if (!ok) break;

@@ -44,6 +44,7 @@ struct DecodeArgs {
   const float *ks, *vs;
   int32_t* hdr;
   const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units
+  int32_t* bnd;            // [grid][8] what the end of each CTA's range cut (written by decode, read by merge)
   float* part_acc;         // [grid * 2][16][D]  numerator * v_scale of a cut item
   float* part_ml;          // [grid * 2][16][2]  running max of the scores, denominator
   float sm_hi, sm_lo;      // softmax scale (natural-log domain) as an unevaluated fp32 pair
@@ -478,7 +479,10 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int total = a.hdr[1], W = a.hdr[2];
   const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
-  if (ubeg >= uend) return;
+  if (ubeg >= uend) {
+    if (tid == 0) a.bnd[blockIdx.x * 8] = -1;   // nothing is cut at the end of an empty range
+    return;
+  }
 
   // Lane-constant pieces of the ldmatrix addresses.
   // K (non-transposed, 4 matrices of 8 keys x 16 channels): lane l addresses key (l & 7) of matrix l >> 3.
@@ -733,6 +737,18 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       KVQ_TL(7);
       u += c1 - c0;
       first_seg = false;
+      if (u == uend && tid == 0) {
+        // Boundary record for the merge kernel: the item this CTA's range ends inside of, if this is the first CTA
+        // boundary inside that item (an item cut several times is merged once, by its first boundary).
+        const int A = p0 + item * nchunks;
+        int4* rec = reinterpret_cast<int4*>(a.bnd + blockIdx.x * 8);
+        if (c1 < nchunks && A >= ubeg) {
+          rec[0] = make_int4(req, kvh, mg, A);
+          rec[1] = make_int4(A + nchunks, tok, qlen, (GS << 8) | rs.mtiles);
+        } else {
+          rec[0] = make_int4(-1, 0, 0, 0);
+        }
+      }
     }
   }
 }
@@ -742,77 +758,70 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 // ------------------------------------------------------------------------------------------------------
 constexpr int MERGE_THREADS = 256;
 
-// One block per (CTA boundary, row). Boundary b is the unit b * W where decode CTA b - 1 stops and CTA b starts;
-// the item that contains it strictly inside was cut there. An item cut by several boundaries is merged by the
-// first of them. The grid therefore depends only on the decode grid, not on the batch. The partials of the
-// item are spread over threads: D / 4 lanes read one partial's row as float4, MERGE_THREADS / (D / 4) partials
-// are in flight per step, so an item cut over hundreds of CTAs (one long request on an otherwise idle GPU)
-// merges in a few dependent load rounds.
+// One block per (CTA boundary, row of an m tile). Boundary b is the unit b * W where decode CTA b - 1 stops and CTA b
+// starts; CTA b - 1 left a record saying which item (if any) it cut there as the first boundary inside the
+// item, so an item cut by several boundaries is merged once and blocks of other boundaries exit after one load.
+// The grid depends only on the decode grid, not on the batch. The partials of an item are spread over threads:
+// D / 4 lanes read one partial's row as float4, MERGE_THREADS / (D / 4) partials are in flight per step, so an item
+// cut over hundreds of CTAs (one long request on an otherwise idle GPU) merges in a few dependent load rounds.
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a) {
   constexpr int LPP = D / 4, PG = MERGE_THREADS / LPP;   // lanes per partial, partials per step
   __shared__ float s_red[MERGE_THREADS / 32];
   __shared__ float4 s_num[PG][LPP];
   __shared__ float s_den[PG];
-  __shared__ int s_req;
-  const int row = blockIdx.y, tid = threadIdx.x;
-  const int total = a.hdr[1], W = a.hdr[2];
-  const int64_t u64 = static_cast<int64_t>(blockIdx.x + 1) * W;
-  if (u64 >= total) return;
-  const int u = static_cast<int>(u64);
-  for (int r = tid; r < a.num_seqs; r += MERGE_THREADS)
-    if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
-  __syncthreads();
-  const int req = s_req;
-  const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok;
-  const ReqShape rs = req_shape(qlen, a.seq_lens[req], a.G, a.Hkv, a.qmax, a.grouped);
-  const int nchunks = rs.nchunks, p0 = a.prefix[req];
-  const int item = (u - p0) / nchunks, kvh = item / rs.mgroups, mg = item - kvh * rs.mgroups;
-  const int A = p0 + item * nchunks, B = A + nchunks;
-  const int c_lo = A / W, c_hi = (B - 1) / W;
-  if (A == u || c_lo != static_cast<int>(blockIdx.x)) return;  // not cut here, or an earlier boundary merges it
-  const int mts = mg * rs.gs + (row >> 4);   // partial row = (m tile of the group) * 16 + row of the tile
-  const int R = mts * 16 + (row & 15), rt = R / a.G, rh = R - rt * a.G;
-  if ((row >> 4) >= rs.gs || mts >= rs.mtiles || rt >= qlen) return;
-  // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
-  auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
+  const int4 r0 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8);
+  if (r0.x < 0) return;
+  const int4 r1 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8 + 4);
+  const int kvh = r0.y, mg = r0.z, A = r0.w, B = r1.x, tok = r1.y, qlen = r1.z, gs = r1.w >> 8, mtiles = r1.w & 0xff;
+  const int W = a.hdr[2], tid = threadIdx.x;
+  const int c_lo = blockIdx.x, c_hi = (B - 1) / W;
   const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
+  for (int sl = 0; sl < gs; ++sl) {   // the m tiles of the item's group; uniform over the block
+    const int row = sl * 16 + blockIdx.y;
+    const int mts = mg * gs + sl;       // partial row = (m tile of the group) * 16 + row of the tile
+    const int R = mts * 16 + blockIdx.y, rt = R / a.G, rh = R - rt * a.G;
+    if (mts >= mtiles || rt >= qlen) continue;
+    // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
+    auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
 
-  float M = -1e30f;
-  for (int i = tid; i < np; i += MERGE_THREADS) M = fmaxf(M, a.part_ml[slot_of(c_lo + i) * 2]);
+    float M = -1e30f;
+    for (int i = tid; i < np; i += MERGE_THREADS) M = fmaxf(M, a.part_ml[slot_of(c_lo + i) * 2]);
 #pragma unroll
-  for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-  if (lane == 0) s_red[warp] = M;
-  __syncthreads();
+    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) s_red[warp] = M;
+    __syncthreads();
 #pragma unroll
-  for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
 
-  const int pg = tid / LPP, l4 = tid - pg * LPP;
-  float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
-  float den = 0.f;
+    const int pg = tid / LPP, l4 = tid - pg * LPP;
+    float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+    float den = 0.f;
 #pragma unroll 4
-  for (int i = pg; i < np; i += PG) {
-    const int sl = slot_of(c_lo + i);
-    const float w = ex2((a.part_ml[sl * 2] - M) * LOG2E);
-    const float4 x = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(sl) * D + l4 * 4);
-    num.x += w * x.x, num.y += w * x.y, num.z += w * x.z, num.w += w * x.w;
-    den += w * a.part_ml[sl * 2 + 1];
-  }
-  s_num[pg][l4] = num;
-  if (l4 == 0) s_den[pg] = den;
-  __syncthreads();
-  if (tid < LPP) {
-    float4 t = s_num[0][tid];
-    float dsum = s_den[0];
-#pragma unroll
-    for (int g = 1; g < PG; ++g) {   // fixed order: the result does not depend on scheduling
-      const float4 x = s_num[g][tid];
-      t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
-      dsum += s_den[g];
+    for (int i = pg; i < np; i += PG) {
+      const int ps = slot_of(c_lo + i);
+      const float w = ex2((a.part_ml[ps * 2] - M) * LOG2E);
+      const float4 x = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(ps) * D + l4 * 4);
+      num.x += w * x.x, num.y += w * x.y, num.z += w * x.z, num.w += w * x.w;
+      den += w * a.part_ml[ps * 2 + 1];
     }
-    const float inv = 1.f / fmaxf(dsum, 1e-30f);
-    *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + tid * 4) =
-        make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
+    s_num[pg][l4] = num;
+    if (l4 == 0) s_den[pg] = den;
+    __syncthreads();
+    if (tid < LPP) {
+      float4 t = s_num[0][tid];
+      float dsum = s_den[0];
+#pragma unroll
+      for (int g = 1; g < PG; ++g) {   // fixed order: the result does not depend on scheduling
+        const float4 x = s_num[g][tid];
+        t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
+        dsum += s_den[g];
+      }
+      const float inv = 1.f / fmaxf(dsum, 1e-30f);
+      *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + tid * 4) =
+          make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
+    }
+    __syncthreads();   // s_red / s_num are reused by the next m tile
   }
 }
 
@@ -936,12 +945,13 @@ cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;  // optional profiling br
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t prefix, part_acc, part_ml, total;
+  size_t prefix, bnd, part_acc, part_ml, total;
 };
 WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas, int part_rows) {
   WorkspaceLayout w;
   w.prefix = HDR_BYTES;
-  w.part_acc = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
+  w.bnd = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
+  w.part_acc = w.bnd + align_up(static_cast<size_t>(max_ctas) * 32, 256);
   w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * part_rows * D * 4;
   w.total = w.part_ml + static_cast<size_t>(max_ctas) * 2 * part_rows * 2 * 4;
   return w;
@@ -1018,6 +1028,7 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   auto* ws = static_cast<uint8_t*>(workspace);
   a.hdr = reinterpret_cast<int32_t*>(ws);
   a.prefix = reinterpret_cast<const int32_t*>(ws + wl.prefix);
+  a.bnd = reinterpret_cast<int32_t*>(ws + wl.bnd);
   a.part_acc = reinterpret_cast<float*>(ws + wl.part_acc);
   a.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
   a.sm_hi = static_cast<float>(softmax_scale);
@@ -1047,14 +1058,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     else
       decode_kernel<128, false><<<grid, NTHREADS, Geom<128, false>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, a.part_rows), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
   } else {
     if (rows16)
       decode_kernel<64, true><<<grid, NTHREADS, Geom<64, true>::SMEM, s>>>(a, tm_k, tm_v);
     else
       decode_kernel<64, false><<<grid, NTHREADS, Geom<64, false>::SMEM, s>>>(a, tm_k, tm_v);
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, a.part_rows), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;

@@ -121,6 +121,12 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
+// predecessor still runs; it must wait here before touching anything the predecessor (or earlier work) wrote.
+// The predecessor lets dependents start early with pdl_launch_dependents(). Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -199,6 +205,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
   __shared__ int s_warp[8];
   __shared__ int s_carry;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();   // the attention kernel may set itself up while the plan is computed
   if (tid == 0) s_carry = 0, hdr[0] = 0;
   __syncthreads();
   for (int base = 0; base < num_seqs; base += 256) {
@@ -477,6 +484,14 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   float* s_acc = reinterpret_cast<float*>(ring_ptr);  // [NWARPS][NROWS][ACC_RS], valid between chunk loops
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  // Barriers start out partitioned for single-warp groups (decode); re-partitioned below if a request needs more.
+  if (tid == 0) {
+    for (int i = 0; i < NSTG; ++i) mbar_init(smem_u32(&s_full[i]), 1), mbar_init(smem_u32(&s_empty[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  fence_proxy_async();   // ordered before the first TMA issue by the __syncthreads of the request search below
+  pdl_wait();            // everything above overlapped the plan kernel; its results are read from here on
+  pdl_launch_dependents();
   const int total = a.hdr[1], W = a.hdr[2];
   const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
   if (ubeg >= uend) {
@@ -491,12 +506,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   const int krow = lane & 7, kmat = lane >> 3;
   const int vrow = (lane & 1) + 8 * ((lane >> 1) & 1) + 2 * ((lane >> 2) & 3) + 16 * (lane >> 4);
 
-  // Barriers start out partitioned for single-warp groups (decode); re-partitioned below if a request needs more.
-  if (tid == 0) {
-    for (int i = 0; i < NSTG; ++i) mbar_init(smem_u32(&s_full[i]), 1), mbar_init(smem_u32(&s_empty[i]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  fence_proxy_async();   // ordered before the first TMA issue by the __syncthreads of the request search below
   int cur_gs = 1;      // group size the barriers are currently initialised for
   int cst = 0, cpass = 0;  // consumer position of this warp's group in its ring: stage, completed passes
   bool ok = true;
@@ -770,6 +779,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   __shared__ float s_red[MERGE_THREADS / 32];
   __shared__ float4 s_num[PG][LPP];
   __shared__ float s_den[PG];
+  pdl_wait();   // the records and partials below are written by the attention kernel
   const int4 r0 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8);
   if (r0.x < 0) return;
   const int4 r1 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8 + 4);
@@ -940,6 +950,19 @@ int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t 
   return KVQ_OK;
 }
 
+// Launch with programmatic stream serialization: the kernel may begin while the previous kernel on the stream is
+// still running and synchronises itself with pdl_wait().
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;  // optional profiling brackets around decode_kernel
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -1054,18 +1077,18 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   if (head_dim == 128) {
     if (rows16)
-      decode_kernel<128, true><<<grid, NTHREADS, Geom<128, true>::SMEM, s>>>(a, tm_k, tm_v);
+      KVQ_CUDA(launch_pdl(decode_kernel<128, true>, dim3(grid), dim3(NTHREADS), Geom<128, true>::SMEM, s, a, tm_k, tm_v));
     else
-      decode_kernel<128, false><<<grid, NTHREADS, Geom<128, false>::SMEM, s>>>(a, tm_k, tm_v);
+      KVQ_CUDA(launch_pdl(decode_kernel<128, false>, dim3(grid), dim3(NTHREADS), Geom<128, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<128><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(grid - 1, PART_ROWS), dim3(MERGE_THREADS), 0, s, a));
   } else {
     if (rows16)
-      decode_kernel<64, true><<<grid, NTHREADS, Geom<64, true>::SMEM, s>>>(a, tm_k, tm_v);
+      KVQ_CUDA(launch_pdl(decode_kernel<64, true>, dim3(grid), dim3(NTHREADS), Geom<64, true>::SMEM, s, a, tm_k, tm_v));
     else
-      decode_kernel<64, false><<<grid, NTHREADS, Geom<64, false>::SMEM, s>>>(a, tm_k, tm_v);
+      KVQ_CUDA(launch_pdl(decode_kernel<64, false>, dim3(grid), dim3(NTHREADS), Geom<64, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) merge_kernel<64><<<dim3(grid - 1, PART_ROWS), MERGE_THREADS, 0, s>>>(a);
+    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(grid - 1, PART_ROWS), dim3(MERGE_THREADS), 0, s, a));
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;

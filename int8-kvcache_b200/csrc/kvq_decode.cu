@@ -52,6 +52,7 @@ struct DecodeArgs {
   int64_t q_st, q_sh, o_st, o_sh, bt_stride;
   int pc_k, pc_v;
   int grouped;             // 1: warps of a CTA share K/V streams across m tiles (multi-token queries)
+  int hg;                  // 0, or 2 / 4: decode with warps of a group on ADJACENT KV HEADS of one stream (see req_shape)
   int part_rows;           // rows per partial slot: 16, or 64 in grouped mode
   int kpos[3], vpos[3];    // tensor-map coordinate slot (1..3) of the (slot-in-block, head, block) dims
 };
@@ -174,22 +175,33 @@ __device__ __forceinline__ float score(int dot, float hi, float lo) {
 
 // Byte offset of (key row tau, 16-byte column c16) inside a TMA-written tile of D-byte rows. The tile base
 // is 1024-byte aligned; TMA's 128B swizzle XORs address bits [4:6] with bits [7:9] (64B: bits [4:5] with [7:8]).
+// A tile is two TMA boxes of 16 keys; a box holds hs heads per key ([key][head][D], hs = 1 except in head-group
+// mode) and this warp reads head hsel of it.
 template <int D>
-__device__ __forceinline__ uint32_t tile_off(int tau, int c16) {
-  const uint32_t off = tau * D + c16 * 16;
+__device__ __forceinline__ uint32_t tile_off(int tau, int c16, int hs = 1, int hsel = 0) {
+  const uint32_t off = ((tau >> 4) * 16 * hs + (tau & 15) * hs + hsel) * D + c16 * 16;
   return off ^ (((off >> 7) & (D == 128 ? 7u : 3u)) << 4);
 }
 
 // Work of one request. A request with q_len query tokens has ceil(q_len * G / 16) m tiles of 16 (token, head) rows
-// per kv head. In grouped mode gs warps share one K/V stream and take one m tile each, so an item is a
-// (kv head, group of gs m tiles) pair; otherwise gs = 1 and every m tile is its own item. Units = 32-key chunks.
+// per kv head. Units are 32-key chunks of items; what an item is depends on the mode:
+//   plain      (kv head, m tile)
+//   grouped    (kv head, group of gs m tiles): gs warps share one K/V stream and take one m tile each
+//   hg = 2, 4  (group of hg adjacent kv heads), decode only: one stream carries the K/V rows of hg heads (a token's
+//              heads are contiguous in a token-major cache, so every TMA box reads hg x head_dim contiguous bytes per
+//              key instead of head_dim) and each of the gs = hg warps takes one head
 struct ReqShape {
   int nchunks, mtiles, gs, mgroups, units;
 };
-__device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped) {
+__device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped, int hg) {
   ReqShape r;
   r.nchunks = max(1, (L + CHUNK - 1) / CHUNK);
   r.mtiles = (qlen * G + 15) / 16;
+  if (hg) {
+    r.gs = hg, r.mgroups = 1;
+    r.units = (qlen < 1 || qlen > qmax) ? 0 : r.nchunks * (Hkv / hg);
+    return r;
+  }
   r.gs = grouped ? (r.mtiles >= 3 ? 4 : (r.mtiles == 2 ? 2 : 1)) : 1;
   r.mgroups = (r.mtiles + r.gs - 1) / r.gs;
   r.units = (qlen < 1 || qlen > qmax) ? 0 : r.nchunks * Hkv * r.mgroups;
@@ -200,7 +212,7 @@ __device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, i
 // plan: units per request, exclusive prefix sum, units per CTA
 // ------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_lens,
-                                                   int num_seqs, int G, int Hkv, int qmax, int grouped, int nctas,
+                                                   int num_seqs, int G, int Hkv, int qmax, int grouped, int hg, int nctas,
                                                    int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
   __shared__ int s_warp[8];
   __shared__ int s_carry;
@@ -211,7 +223,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
   for (int base = 0; base < num_seqs; base += 256) {
     const int r = base + tid;
     int u = 0;
-    if (r < num_seqs) u = req_shape(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, grouped).units;
+    if (r < num_seqs) u = req_shape(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, grouped, hg).units;
     int x = u;  // inclusive scan inside the warp
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -251,7 +263,7 @@ struct Geom {
   static constexpr int STAGE = 2 * TILE;          // K chunk + V chunk
   static constexpr int NSTG = NWARPS * NSTAGE;    // stages per CTA
   static constexpr int RING = NSTG * STAGE;
-  static constexpr int SLOTS = ROWS16 ? NWARPS : 1;  // m tiles a CTA can hold q for
+  static constexpr int SLOTS = NWARPS;            // m tiles (or kv heads of a head group) a CTA holds q for
   static constexpr int QROW = D + 16;             // s_q row stride: conflict-free A-fragment loads
   static constexpr int ACC_RS = D + 8;            // combine buffer row stride in floats
   static constexpr int SMALL = SLOTS * 16 * QROW + 6 * 64 * 4;
@@ -364,7 +376,7 @@ struct TileState {
 // swizzled K and V tiles; n_base: absolute position of the chunk's first key.
 template <int D, bool ROWS16>
 __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk, uint32_t sv, int n_base, int lim_all,
-                                           int krow, int kmat, int vrow, int t) {
+                                           int krow, int kmat, int vrow, int t, int hs, int hsel) {
   constexpr int KSTEPS = D / 32, NT = D / 8;
   // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
   int sacc[4][4];
@@ -374,7 +386,7 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
 #pragma unroll
     for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
       uint32_t b[4];
-      ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat));
+      ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
       mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
       mma_s8(sacc[j], s.qa[2 * s2 + 1], b[2], b[3]);
     }
@@ -445,7 +457,7 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
 #pragma unroll
   for (int jp = 0; jp < NT / 2; ++jp) {
     uint32_t b[4];
-    ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp));
+    ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp, hs, hsel));
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
       int pacc[4] = {0, 0, 0, 0};
@@ -520,7 +532,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     const int req = s_req;
     KVQ_TL(1);
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
-    const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped);
+    const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, a.hg);
     const int nchunks = rs.nchunks;
     const int p0 = a.prefix[req], p1 = a.prefix[req + 1];
     const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
@@ -528,7 +540,13 @@ __global__ void __launch_bounds__(NTHREADS, 2)
     // ---- warp groups for this request; the ring and its barriers are re-partitioned when the group size changes
     //      (everything issued so far has been consumed at this point) ----
     const int GS = rs.gs, lgs = GS >> 1 /* log2 of 1, 2, 4 */, NG = NWARPS >> lgs, gidx = warp >> lgs,
-              msl = warp & (GS - 1), RD = NSTAGE * GS;
+              msl = warp & (GS - 1);
+    // Ring geometry of a group. m-tile groups: 3 * GS stages of one chunk of one head; head groups: 3 stages of one
+    // chunk of GS heads. Either way the group owns 3 * GS * STAGE bytes and keeps PD chunks in flight.
+    const int HS = a.hg ? GS : 1;                                 // heads per TMA box
+    const int RD = a.hg ? NSTAGE : NSTAGE * GS;                   // stages in the ring
+    const int PD = a.hg ? NSTAGE - 1 : (NSTAGE - 1) * GS;         // prefetch distance, in chunks of the group
+    const uint32_t SB = HS * Gm::STAGE;                           // bytes per stage
     if (GS != cur_gs) {
       if (tid == 0) {
         for (int i = 0; i < NSTG; ++i) {
@@ -543,19 +561,21 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       cur_gs = GS;
       cst = 0, cpass = 0;
     }
-    const uint32_t gring = ring + gidx * RD * Gm::STAGE;
-    const uint32_t gfull = smem_u32(&s_full[gidx * RD]), gempty = smem_u32(&s_empty[gidx * RD]);
+    const uint32_t gring = ring + gidx * NSTAGE * GS * Gm::STAGE;
+    const uint32_t gfull = smem_u32(&s_full[gidx * NSTAGE * GS]), gempty = smem_u32(&s_empty[gidx * NSTAGE * GS]);
 
     // ---- items (kv head, m-tile group) of this request that intersect [u, uend) ----
     while (u < uend && u < p1) {
       const int item = (u - p0) / nchunks, c0 = (u - p0) - item * nchunks;
-      const int kvh = item / rs.mgroups, mg = item - kvh * rs.mgroups;
+      const int kv_base = a.hg ? item * GS : item / rs.mgroups;       // first (or only) kv head of the item
+      const int mg = a.hg ? 0 : item - kv_base * rs.mgroups;           // m-tile group of the item
+      const int kvh = kv_base + (a.hg ? msl : 0);                      // this warp's kv head
       const int c1 = min(nchunks, c0 + (uend - u));
       const bool whole = (c0 == 0 && c1 == nchunks);
       // the group consumes chunks c0 + gidx + NG * i, i < nig; inside the group warp msl produces i = msl + GS * ip
       const int nig = (c1 - c0 - gidx + NG - 1) / NG;
       const int npw = (nig - msl + GS - 1) >> lgs;
-      const int mtw = mg * GS + msl;                 // this warp's m tile
+      const int mtw = a.hg ? 0 : mg * GS + msl;      // this warp's m tile
       const bool active = mtw < rs.mtiles;
 
       // -- TMA producer: page ids 16 chunks at a time, one lane per 16-key half chunk --
@@ -584,18 +604,18 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         if (GS > 1 && prev_pass >= 0)   // the other warps of the group must have left the stage's previous contents
           ok = ok && __all_sync(0xffffffffu, mbar_wait(gempty + st * 8, prev_pass & 1));
         if (lane == 0 && ok) {
-          const uint32_t bar = gfull + st * 8, dst = gring + st * Gm::STAGE;
+          const uint32_t bar = gfull + st * 8, dst = gring + st * SB;
           const int c = chunk_of(ip);
-          mbar_expect_tx(bar, Gm::STAGE);
+          mbar_expect_tx(bar, SB);
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             const int n0 = c * CHUNK + half * 16;
             const int off = (n0 < L ? n0 : c * CHUNK) & a.bs_mask;
             const int page = half ? pb : pa;
             // coordinate slot s holds whichever of (offset in block, head, block) the tensor map put there
-            auto coord = [&](const int (&pos)[3], int s) { return pos[0] == s ? off : (pos[1] == s ? kvh : page); };
-            tma_load_4d(dst + half * 16 * D, &tm_k, 0, coord(a.kpos, 1), coord(a.kpos, 2), coord(a.kpos, 3), bar);
-            tma_load_4d(dst + Gm::TILE + half * 16 * D, &tm_v, 0, coord(a.vpos, 1), coord(a.vpos, 2),
+            auto coord = [&](const int (&pos)[3], int s) { return pos[0] == s ? off : (pos[1] == s ? kv_base : page); };
+            tma_load_4d(dst + half * 16 * HS * D, &tm_k, 0, coord(a.kpos, 1), coord(a.kpos, 2), coord(a.kpos, 3), bar);
+            tma_load_4d(dst + SB / 2 + half * 16 * HS * D, &tm_v, 0, coord(a.vpos, 1), coord(a.vpos, 2),
                         coord(a.vpos, 3), bar);
           }
         }
@@ -604,7 +624,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       // bulk loads (~200 KB per SM) a plain load waits for microseconds; ahead of it, it costs one round trip.
       uint2 q_early[NROWS / NWARPS];
       float sk_early[4];
-      if constexpr (!ROWS16) {
+      const bool early_q = !ROWS16 && GS == 1;
+      if (early_q) {
         q_load_scale<D>(a, kvh, lane, sk_early);
 #pragma unroll
         for (int k = 0; k < NROWS / NWARPS; ++k)
@@ -613,19 +634,21 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       // A single-warp group refills a stage right after consuming it, so it can fill its whole ring now and keep
       // HBM busy through the q prologue; a shared ring keeps one stage back for the other warps of the group.
       if (ok)
-        for (int ip = 0; ip < min(npw, GS == 1 ? NSTAGE : NSTAGE - 1); ++ip) issue(ip, msl + GS * ip);
+        for (int ip = 0; ip < npw && msl + GS * ip < (GS == 1 ? NSTAGE : PD); ++ip) issue(ip, msl + GS * ip);
       KVQ_TL(2);
 
       // -- q prologue for every m tile of the group --
-      if constexpr (!ROWS16) {
+      if (early_q) {
 #pragma unroll
         for (int k = 0; k < NROWS / NWARPS; ++k)
           q_quantize_row<D>(a, q_early[k], sk_early, s_q, s_chi, s_clo, kvh, warp + NWARPS * k, lane);
       } else {
-        for (int sl = 0; sl < GS; ++sl)
-          if (mg * GS + sl < rs.mtiles)
-            q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen, kvh,
-                                 mg * GS + sl, warp, lane);
+        for (int sl = 0; sl < GS; ++sl) {   // slot = m tile of the group, or kv head of the head group
+          const int mts = a.hg ? 0 : mg * GS + sl;
+          if (mts < rs.mtiles)
+            q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen,
+                                 kv_base + (a.hg ? sl : 0), mts, warp, lane);
+        }
       }
       __syncthreads();
       TileState<D, ROWS16> ts;
@@ -657,16 +680,18 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 
       // -- main loop over the group's chunks --
       for (int i = 0; i < nig && ok; ++i) {
-        const int ipn = (i >> lgs) + NSTAGE - 1;       // shared ring: keep NSTAGE - 1 of my chunks in flight
+        // keep PD chunks of the group in flight: chunk i + PD is issued by the warp whose turn it is
         // (a single-warp group pre-issued NSTAGE chunks, so its first in-loop issue is chunk NSTAGE at i == 1)
-        if ((i & (GS - 1)) == msl && ipn < npw && (GS > 1 || i > 0)) issue(ipn, (NSTAGE - 1) * GS);
+        const int jn = i + PD;
+        if ((jn & (GS - 1)) == msl && jn < nig && (GS > 1 || i > 0)) issue(jn >> lgs, PD);
         const int st = cst;
         ok = ok && __all_sync(0xffffffffu, mbar_wait(gfull + st * 8, cpass & 1));
         if (!ok) break;
         if (i == 0) KVQ_TL(4);
         if (active) {
-          const uint32_t sk = gring + st * Gm::STAGE;
-          chunk_step<D, ROWS16>(ts, sk, sk + Gm::TILE, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t);
+          const uint32_t sk = gring + st * SB;
+          chunk_step<D, ROWS16>(ts, sk, sk + SB / 2, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t, HS,
+                                a.hg ? msl : 0);
         }
         __syncwarp();  // every lane is done with this stage before it is refilled
         if (GS > 1 && lane == 0) mbar_arrive(gempty + st * 8);
@@ -710,7 +735,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       for (int i = tid; i < GS * NROWS * (D / 4); i += NTHREADS) {
         const int sl = i / (NROWS * (D / 4)), rem = i - sl * (NROWS * (D / 4));
         const int row = rem / (D / 4), c4 = (rem - row * (D / 4)) * 4;
-        const int mts = mg * GS + sl;
+        const int mts = a.hg ? 0 : mg * GS + sl, kvs = kv_base + (a.hg ? sl : 0);   // m tile and kv head of the slot
         const int R = mts * 16 + row, rt = R / a.G, rh = R - rt * a.G;
         if (mts >= rs.mtiles || rt >= qlen) continue;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -720,16 +745,16 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         }
         float4 sv4;
         if (a.pc_v) {
-          sv4 = __ldg(reinterpret_cast<const float4*>(a.vs + kvh * D + c4));
+          sv4 = __ldg(reinterpret_cast<const float4*>(a.vs + kvs * D + c4));
         } else {
-          const float one = __ldg(a.vs + kvh);
+          const float one = __ldg(a.vs + kvs);
           sv4 = make_float4(one, one, one, one);
         }
         if (whole) {
           const float inv = s_inv[sl * 16 + row];
           const uint2 o = make_uint2(pack_bf16x2(v.x * inv * sv4.x, v.y * inv * sv4.y),
                                      pack_bf16x2(v.z * inv * sv4.z, v.w * inv * sv4.w));
-          *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + c4) = o;
+          *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvs * a.G + rh) * a.o_sh + c4) = o;
         } else {
           const int prow = slot_base + sl * 16 + row;
           *reinterpret_cast<float4*>(a.part_acc + static_cast<int64_t>(prow) * D + c4) =
@@ -752,7 +777,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         const int A = p0 + item * nchunks;
         int4* rec = reinterpret_cast<int4*>(a.bnd + blockIdx.x * 8);
         if (c1 < nchunks && A >= ubeg) {
-          rec[0] = make_int4(req, kvh, mg, A);
+          rec[0] = make_int4(req, kv_base, mg, A);
           rec[1] = make_int4(A + nchunks, tok, qlen, (GS << 8) | rs.mtiles);
         } else {
           rec[0] = make_int4(-1, 0, 0, 0);
@@ -789,7 +814,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
   for (int sl = 0; sl < gs; ++sl) {   // the m tiles of the item's group; uniform over the block
     const int row = sl * 16 + blockIdx.y;
-    const int mts = mg * gs + sl;       // partial row = (m tile of the group) * 16 + row of the tile
+    const int mts = a.hg ? 0 : mg * gs + sl;   // partial row = slot * 16 + row of the tile; slot = m tile or kv head
+    const int kvs = kvh + (a.hg ? sl : 0);
     const int R = mts * 16 + blockIdx.y, rt = R / a.G, rh = R - rt * a.G;
     if (mts >= mtiles || rt >= qlen) continue;
     // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
@@ -828,7 +854,7 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
         dsum += s_den[g];
       }
       const float inv = 1.f / fmaxf(dsum, 1e-30f);
-      *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvh * a.G + rh) * a.o_sh + tid * 4) =
+      *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvs * a.G + rh) * a.o_sh + tid * 4) =
           make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
     }
     __syncthreads();   // s_red / s_num are reused by the next m tile
@@ -855,9 +881,10 @@ EncodeFn g_encode = nullptr;
 struct MapKey {
   const void* ptr;
   int64_t nb, sb, sn, sh;
-  int bs, H, D;
+  int bs, H, D, box_heads;
   bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && nb == o.nb && sb == o.sb && sn == o.sn && sh == o.sh && bs == o.bs && H == o.H && D == o.D;
+    return ptr == o.ptr && nb == o.nb && sb == o.sb && sn == o.sn && sh == o.sh && bs == o.bs && H == o.H && D == o.D &&
+           box_heads == o.box_heads;
   }
 };
 struct MapEntry {
@@ -906,9 +933,10 @@ int device_info(DeviceInfo** out) {
 
 // Tensor map over a cache view [nb, bs, H, D] (int8). TMA wants ascending-friendly dims; the three outer dims are
 // ordered by stride and pos[] tells the kernel which coordinate slot holds (slot-in-block, head, block).
+// box_heads > 1 (head-group mode) needs adjacent heads (sh == D): the box is then [16 slots][box_heads][D] in smem.
 int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t sb, int64_t sn, int64_t sh,
-                     CUtensorMap* map, int* pos) {
-  const MapKey key{ptr, nb, sb, sn, sh, bs, H, D};
+                     int box_heads, CUtensorMap* map, int* pos) {
+  const MapKey key{ptr, nb, sb, sn, sh, bs, H, D, box_heads};
   std::lock_guard<std::mutex> lock(g_mu);
   for (const MapEntry& e : g_maps)
     if (e.key == key) {
@@ -921,7 +949,7 @@ int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t 
     uint64_t size, stride;
     uint32_t box;
   } dims[3] = {{0, static_cast<uint64_t>(bs), static_cast<uint64_t>(sn), 16u},
-               {1, static_cast<uint64_t>(H), static_cast<uint64_t>(sh), 1u},
+               {1, static_cast<uint64_t>(H), static_cast<uint64_t>(sh), static_cast<uint32_t>(box_heads)},
                {2, static_cast<uint64_t>(nb), static_cast<uint64_t>(sb), 1u}};
   for (Dim& d : dims)
     if (d.size == 1) d.stride = static_cast<uint64_t>(D);  // the stride of a size-1 dim is never used
@@ -936,7 +964,9 @@ int cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t 
   e.key = key;
   const CUresult r = g_encode(&e.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), gdim, gstr, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, D == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                              D == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_64B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              box_heads > 1 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B
+                                            : (D == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B : CU_TENSOR_MAP_L2_PROMOTION_L2_64B),
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error("cuTensorMapEncodeTiled failed with CUresult %d (cache strides %lld/%lld/%lld)", static_cast<int>(r),
               static_cast<long long>(sb), static_cast<long long>(sn), static_cast<long long>(sh));
@@ -1039,6 +1069,17 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   const int mtiles_max = (G * max_q + 15) / 16;
   WorkspaceLayout wl = workspace_layout(num_seqs, head_dim, grid, PART_ROWS_GROUPED);
   int grouped = rows16 && mtiles_max >= 2 && workspace_bytes >= wl.total;
+  // Head groups: single-tile decode over a token-major cache whose heads are adjacent in memory. With 8 or more
+  // kv heads a (page, head) tile is 16 rows of head_dim bytes at a pitch of >= 1 KB, which HBM serves at ~75 % of
+  // its rate; one stream per pair of adjacent heads reads 2 x head_dim contiguous bytes per key instead (measured
+  // at Hkv = 8: 4.9 -> 5.9 TB/s with pairs, 5.1 TB/s with groups of four, which leave too few streams per SM;
+  // at Hkv = 4 the plain mode is already at the HBM rate).
+  int hg = 0;
+  if (!rows16 && workspace_bytes >= wl.total && kc_stride_h == head_dim && vc_stride_h == head_dim &&
+      kc_stride_n >= static_cast<int64_t>(num_kv_heads) * head_dim &&
+      vc_stride_n >= static_cast<int64_t>(num_kv_heads) * head_dim && num_kv_heads >= 8 && num_kv_heads % 2 == 0)
+    hg = 2;
+  if (hg) grouped = 1;
   if (!grouped) wl = workspace_layout(num_seqs, head_dim, grid, PART_ROWS);
   if (!workspace || workspace_bytes < wl.total || (reinterpret_cast<uintptr_t>(workspace) & 255)) {
     set_error("decode workspace: need %zu bytes aligned to 256, got %zu at %p", wl.total, workspace_bytes, workspace);
@@ -1062,17 +1103,17 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   a.bs_mask = block_size - 1;
   a.q_st = q_stride_t, a.q_sh = q_stride_h, a.o_st = o_stride_t, a.o_sh = o_stride_h, a.bt_stride = bt_stride;
   a.pc_k = k_per_channel, a.pc_v = v_per_channel;
-  a.grouped = grouped, a.part_rows = grouped ? PART_ROWS_GROUPED : PART_ROWS;
+  a.grouped = grouped, a.hg = hg, a.part_rows = grouped ? PART_ROWS_GROUPED : PART_ROWS;
   CUtensorMap tm_k, tm_v;
   if ((rc = cache_tensor_map(k_cache, num_blocks, block_size, num_kv_heads, head_dim, kc_stride_b, kc_stride_n,
-                             kc_stride_h, &tm_k, a.kpos)) != KVQ_OK)
+                             kc_stride_h, hg ? hg : 1, &tm_k, a.kpos)) != KVQ_OK)
     return rc;
   if ((rc = cache_tensor_map(v_cache, num_blocks, block_size, num_kv_heads, head_dim, vc_stride_b, vc_stride_n,
-                             vc_stride_h, &tm_v, a.vpos)) != KVQ_OK)
+                             vc_stride_h, hg ? hg : 1, &tm_v, a.vpos)) != KVQ_OK)
     return rc;
 
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, grid, a.hdr,
+  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, grid, a.hdr,
                                 reinterpret_cast<int32_t*>(ws + wl.prefix));
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   if (head_dim == 128) {

@@ -22,7 +22,9 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, os.path.join(ROOT, "int8-kvcache_b200"))
-sys.path.insert(0, os.environ.get("KVQ_REF", "/root/reference"))
+if "KVQ_REF" not in os.environ:
+    raise SystemExit("set KVQ_REF to a checkout of the reference project (ischencheng/int8-kvcache)")
+sys.path.insert(0, os.environ["KVQ_REF"])
 
 from kvq import cuda_kernels as ref_ck  # noqa: E402
 from kvq import quant as ref_quant  # noqa: E402

@@ -69,7 +69,7 @@ def test_quant_cache_golden(d, gran, layout):
 
 
 def test_quant_cache_config1_round_trip():
-    """BASELINE config 1: 8192 tokens into a 65536-slot cache, bit-exact against the oracle, then the pages
+    """Benchmark configuration 1 (cache write round trip): 8192 tokens into a 65536-slot cache, bit-exact against the oracle, then the pages
     dequantized back to bf16 (also bit-exact). A strided key (fused qkv row stride) is used."""
     c = workloads.config1()
     st, bs, nb = c["static"], c["block_size"], c["num_blocks"]
@@ -161,7 +161,7 @@ def test_attention_golden(name):
 
 
 def test_attention_config0_golden():
-    """BASELINE config 0 (4 requests, contexts 128..512): reference output, then the bf16 golden within the
+    """Benchmark configuration 0 (4 requests, contexts 128..512): reference output, then the bf16 golden within the
     reference's own quantization tolerance."""
     fx = load_golden("attn_config0.npz")
     out = run_decode(workloads.config0())

@@ -29,7 +29,7 @@ def test_attention_matches_reference(name):
 
 
 def test_config0_matches_reference_and_bf16_golden():
-    """BASELINE config 0, inputs regenerated from the seed (checksummed), outputs from the reference."""
+    """Benchmark configuration 0 (4 decode requests, contexts 128..512), inputs regenerated from the seed (checksummed), outputs from the reference."""
     fx = load_golden("attn_config0.npz")
     c = workloads.config0()
     h = hashlib.sha256()

@@ -791,16 +791,21 @@ __global__ void __launch_bounds__(NTHREADS, 2)
 // merge of items that were cut across CTAs
 // ------------------------------------------------------------------------------------------------------
 constexpr int MERGE_THREADS = 256;
+constexpr int MERGE_ROWS = 2;      // rows of an m tile per block: grid.y = 16 / MERGE_ROWS
+constexpr int MERGE_SHALLOW = 8;   // up to this many partials per item: one lane group per row, no block cooperation
 
-// One block per (CTA boundary, row of an m tile). Boundary b is the unit b * W where decode CTA b - 1 stops and CTA b
-// starts; CTA b - 1 left a record saying which item (if any) it cut there as the first boundary inside the
-// item, so an item cut by several boundaries is merged once and blocks of other boundaries exit after one load.
-// The grid depends only on the decode grid, not on the batch. The partials of an item are spread over threads:
-// D / 4 lanes read one partial's row as float4, MERGE_THREADS / (D / 4) partials are in flight per step, so an item
-// cut over hundreds of CTAs (one long request on an otherwise idle GPU) merges in a few dependent load rounds.
+// One block per (CTA boundary, MERGE_ROWS rows of an m tile). Boundary b is the unit b * W where decode CTA b - 1
+// stops and CTA b starts; CTA b - 1 left a record saying which item (if any) it cut there as the first boundary
+// inside the item, so an item cut by several boundaries is merged once and blocks of other boundaries exit after
+// one load. The grid depends only on the decode grid, not on the batch. Two shapes of work:
+//   shallow (the usual case, an item cut into a few partials): each group of D / 4 lanes owns one (m tile, row)
+//     of the item and sums its partials itself, so the m tiles of a group merge side by side without a block barrier;
+//   deep (one long request cut over hundreds of CTAs on an otherwise idle GPU): the partials of a row are spread
+//     over the lane groups, MERGE_THREADS / (D / 4) in flight per step, and reduced through shared memory.
 template <int D>
 __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a) {
-  constexpr int LPP = D / 4, PG = MERGE_THREADS / LPP;   // lanes per partial, partials per step
+  constexpr int LPP = D / 4, PG = MERGE_THREADS / LPP;   // lanes per partial row, lane groups per block
+  static_assert(PG >= NWARPS * MERGE_ROWS, "a lane group per (m tile, row)");
   __shared__ float s_red[MERGE_THREADS / 32];
   __shared__ float4 s_num[PG][LPP];
   __shared__ float s_den[PG];
@@ -812,53 +817,92 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   const int W = a.hdr[2], tid = threadIdx.x;
   const int c_lo = blockIdx.x, c_hi = (B - 1) / W;
   const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
-  for (int sl = 0; sl < gs; ++sl) {   // the m tiles of the item's group; uniform over the block
-    const int row = sl * 16 + blockIdx.y;
-    const int mts = a.hg ? 0 : mg * gs + sl;   // partial row = slot * 16 + row of the tile; slot = m tile or kv head
-    const int kvs = kvh + (a.hg ? sl : 0);
-    const int R = mts * 16 + blockIdx.y, rt = R / a.G, rh = R - rt * a.G;
-    if (mts >= mtiles || rt >= qlen) continue;
-    // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
-    auto slot_of = [&](int c) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
+  const int pg = tid / LPP, l4 = tid - pg * LPP;
+  // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
+  auto slot_of = [&](int c, int row) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
+  // partial row = slot * 16 + row of the tile; slot = m tile of the group, or kv head of a head group
+  auto store = [&](int sl, int r16, float4 t, float den) {
+    const int mts = a.hg ? 0 : mg * gs + sl, kvs = kvh + (a.hg ? sl : 0);
+    const int R = mts * 16 + r16, rt = R / a.G, rh = R - rt * a.G;
+    const float inv = 1.f / fmaxf(den, 1e-30f);
+    *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvs * a.G + rh) * a.o_sh + l4 * 4) =
+        make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
+  };
+  auto live = [&](int sl, int r16) {
+    const int mts = a.hg ? 0 : mg * gs + sl;
+    return mts < mtiles && (mts * 16 + r16) / a.G < qlen;
+  };
 
+  if (np <= MERGE_SHALLOW) {
+    const int sl = pg / MERGE_ROWS, r16 = blockIdx.y * MERGE_ROWS + (pg - sl * MERGE_ROWS);
+    if (sl >= gs || !live(sl, r16)) return;
+    const int row = sl * 16 + r16;
+    float m[MERGE_SHALLOW], l[MERGE_SHALLOW];
+    float4 x[MERGE_SHALLOW];
     float M = -1e30f;
-    for (int i = tid; i < np; i += MERGE_THREADS) M = fmaxf(M, a.part_ml[slot_of(c_lo + i) * 2]);
 #pragma unroll
-    for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-    if (lane == 0) s_red[warp] = M;
-    __syncthreads();
+    for (int i = 0; i < MERGE_SHALLOW; ++i)
+      if (i < np) {   // every load of the row is issued before the first use
+        const int ps = slot_of(c_lo + i, row);
+        m[i] = a.part_ml[ps * 2];
+        l[i] = a.part_ml[ps * 2 + 1];
+        x[i] = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(ps) * D + l4 * 4);
+      }
 #pragma unroll
-    for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
-
-    const int pg = tid / LPP, l4 = tid - pg * LPP;
+    for (int i = 0; i < MERGE_SHALLOW; ++i)
+      if (i < np) M = fmaxf(M, m[i]);
     float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
     float den = 0.f;
-#pragma unroll 4
-    for (int i = pg; i < np; i += PG) {
-      const int ps = slot_of(c_lo + i);
-      const float w = ex2((a.part_ml[ps * 2] - M) * LOG2E);
-      const float4 x = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(ps) * D + l4 * 4);
-      num.x += w * x.x, num.y += w * x.y, num.z += w * x.z, num.w += w * x.w;
-      den += w * a.part_ml[ps * 2 + 1];
-    }
-    s_num[pg][l4] = num;
-    if (l4 == 0) s_den[pg] = den;
-    __syncthreads();
-    if (tid < LPP) {
-      float4 t = s_num[0][tid];
-      float dsum = s_den[0];
 #pragma unroll
-      for (int g = 1; g < PG; ++g) {   // fixed order: the result does not depend on scheduling
-        const float4 x = s_num[g][tid];
-        t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
-        dsum += s_den[g];
+    for (int i = 0; i < MERGE_SHALLOW; ++i)
+      if (i < np) {
+        const float w = ex2((m[i] - M) * LOG2E);
+        num.x += w * x[i].x, num.y += w * x[i].y, num.z += w * x[i].z, num.w += w * x[i].w;
+        den += w * l[i];
       }
-      const float inv = 1.f / fmaxf(dsum, 1e-30f);
-      *reinterpret_cast<uint2*>(a.out + (tok + rt) * a.o_st + (kvs * a.G + rh) * a.o_sh + tid * 4) =
-          make_uint2(pack_bf16x2(t.x * inv, t.y * inv), pack_bf16x2(t.z * inv, t.w * inv));
-    }
-    __syncthreads();   // s_red / s_num are reused by the next m tile
+    store(sl, r16, num, den);
+    return;
   }
+
+  for (int rb = 0; rb < MERGE_ROWS; ++rb)
+    for (int sl = 0; sl < gs; ++sl) {   // uniform over the block
+      const int r16 = blockIdx.y * MERGE_ROWS + rb, row = sl * 16 + r16;
+      if (!live(sl, r16)) continue;
+      float M = -1e30f;
+      for (int i = tid; i < np; i += MERGE_THREADS) M = fmaxf(M, a.part_ml[slot_of(c_lo + i, row) * 2]);
+#pragma unroll
+      for (int o = 16; o; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+      if (lane == 0) s_red[warp] = M;
+      __syncthreads();
+#pragma unroll
+      for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, s_red[w]);
+
+      float4 num = make_float4(0.f, 0.f, 0.f, 0.f);
+      float den = 0.f;
+#pragma unroll 4
+      for (int i = pg; i < np; i += PG) {
+        const int ps = slot_of(c_lo + i, row);
+        const float w = ex2((a.part_ml[ps * 2] - M) * LOG2E);
+        const float4 x = *reinterpret_cast<const float4*>(a.part_acc + static_cast<int64_t>(ps) * D + l4 * 4);
+        num.x += w * x.x, num.y += w * x.y, num.z += w * x.z, num.w += w * x.w;
+        den += w * a.part_ml[ps * 2 + 1];
+      }
+      s_num[pg][l4] = num;
+      if (l4 == 0) s_den[pg] = den;
+      __syncthreads();
+      if (tid < LPP) {
+        float4 t = s_num[0][tid];
+        float dsum = s_den[0];
+#pragma unroll
+        for (int g = 1; g < PG; ++g) {   // fixed order: the result does not depend on scheduling
+          const float4 x = s_num[g][tid];
+          t.x += x.x, t.y += x.y, t.z += x.z, t.w += x.w;
+          dsum += s_den[g];
+        }
+        store(sl, r16, t, dsum);
+      }
+      __syncthreads();   // s_red / s_num are reused by the next row
+    }
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -1122,14 +1166,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     else
       KVQ_CUDA(launch_pdl(decode_kernel<128, false>, dim3(grid), dim3(NTHREADS), Geom<128, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(grid - 1, PART_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(grid - 1, 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
   } else {
     if (rows16)
       KVQ_CUDA(launch_pdl(decode_kernel<64, true>, dim3(grid), dim3(NTHREADS), Geom<64, true>::SMEM, s, a, tm_k, tm_v));
     else
       KVQ_CUDA(launch_pdl(decode_kernel<64, false>, dim3(grid), dim3(NTHREADS), Geom<64, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(grid - 1, PART_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(grid - 1, 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;

@@ -158,6 +158,29 @@ int kvq_dequant_pages(const void* k_cache, const void* v_cache, void* k_out, voi
                       int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
                       int k_per_channel, int v_per_channel, kvq_stream_t stream);
 
+/*
+ * Causal attention for requests with MORE than min_query_len query tokens (prefill, chunked prefill), reading the
+ * INT8 pages directly. Takes the place of the reference's long path as a whole - plan_long + dequant_pages into a
+ * temporary bf16 cache + FlashAttention over it, kvq/cuda_kernels.py:80-131 - and computes the same quantity
+ * ("implementation A", kvq/int8_ref.py:62-91): softmax(q . (k_i8 * k_scale)^T * softmax_scale) . (v_i8 * v_scale)
+ * with the bottom-right causal mask (key n visible to query token t iff n < seq_len - q_len + 1 + t). Requests with
+ * at most min_query_len query tokens are skipped and their output rows left untouched, so a mixed batch is served
+ * by this call followed by kvq_int8_decode_attention with qmax = min_query_len. Arguments as for
+ * kvq_int8_decode_attention; total_query_tokens = rows of q (sizes the grid). The workspace
+ * (kvq_prefill_workspace_size(num_seqs) bytes, 256-byte aligned) holds the status word (int32 [0], non-zero after
+ * an expired wait) and the work plan. Two launches on `stream`, no host synchronization, capturable.
+ */
+size_t kvq_prefill_workspace_size(int num_seqs);
+int kvq_int8_prefill_attention(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
+                               const int32_t* seq_lens, const int32_t* block_table, const float* k_scale,
+                               const float* v_scale, double softmax_scale, int num_seqs, int64_t total_query_tokens,
+                               int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks,
+                               int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t, int64_t o_stride_h,
+                               int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h, int64_t vc_stride_b,
+                               int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride, int k_per_channel,
+                               int v_per_channel, int min_query_len, void* workspace, size_t workspace_bytes,
+                               kvq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

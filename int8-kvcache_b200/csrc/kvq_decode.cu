@@ -23,6 +23,8 @@
 #include <vector>
 
 #include "kvq_common.cuh"
+#include "kvq_host.h"
+#include "kvq_ptx.cuh"
 
 namespace kvq {
 namespace {
@@ -60,49 +62,6 @@ struct DecodeArgs {
 // ------------------------------------------------------------------------------------------------------
 // PTX wrappers
 // ------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_inval(uint32_t bar) {
-  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait: gives up after ~2^31 clock cycles (about a second) and reports failure instead of hanging.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (;;) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > (1ll << 31)) return false;
-  }
-}
-__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
-                                            uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
-      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -122,19 +81,6 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
-// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may start while its
-// predecessor still runs; it must wait here before touching anything the predecessor (or earlier work) wrote.
-// The predecessor lets dependents start early with pdl_launch_dependents(). Both are no-ops in a plain launch.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-__device__ __forceinline__ float ex2(float x) {
-  float y;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
-constexpr float LOG2E = 1.4426950408889634f;
 
 #ifdef KVQ_TIMELINE   // debug builds only: per-CTA cycle stamps of the first item, read back by a probe
 __device__ long long g_timeline[1024 * 16];
@@ -1055,6 +1001,18 @@ WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas, int part_row
 }
 
 }  // namespace
+
+int shared_device_sms(int* sms) {
+  DeviceInfo* di = nullptr;
+  const int rc = device_info(&di);
+  if (rc == KVQ_OK) *sms = di->sms;
+  return rc;
+}
+int shared_cache_tensor_map(const void* ptr, int64_t nb, int bs, int H, int D, int64_t sb, int64_t sn, int64_t sh,
+                            int box_heads, CUtensorMap* map, int* pos) {
+  return cache_tensor_map(ptr, nb, bs, H, D, sb, sn, sh, box_heads, map, pos);
+}
+
 }  // namespace kvq
 
 using namespace kvq;

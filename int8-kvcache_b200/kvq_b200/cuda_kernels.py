@@ -2,9 +2,10 @@
 behaviour as the reference's kvq/cuda_kernels.py, backed by libkvq_b200.so through its C ABI.
 
 Attention on the INT8 cache is routed by query length, as in the reference (kvq/cuda_kernels.py:1-12):
-requests with at most SHORT_Q query tokens run the INT8 tensor-core kernel; longer ones have their pages
-dequantized to a temporary bf16 paged cache that a FlashAttention kernel reads. In a mixed batch the long
-path runs first over every request and the INT8 kernel then overwrites the short requests' rows.
+requests with at most SHORT_Q query tokens run the INT8 tensor-core kernel; longer ones either have their pages
+dequantized to a temporary bf16 paged cache that a FlashAttention kernel reads (the reference's route) or run
+prefill_attention, which reads the INT8 pages directly. In a mixed batch the long path runs first and the INT8
+kernel then writes the short requests' rows.
 
 All tensors must live on the current CUDA device; work is enqueued on torch's current stream, nothing
 synchronizes, and every call can be captured in a CUDA graph.
@@ -260,6 +261,58 @@ def long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table
     return out
 
 
+_PREFILL_WS = {}
+
+
+def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static):
+    """Causal attention for the requests with more than SHORT_Q query tokens, read straight from the INT8 pages
+    (tcgen05 tensor-core kernel; no temporary bf16 cache, no plan). Requests with at most SHORT_Q query tokens are
+    skipped and their rows of `out` left untouched. Same result as long_attention up to bf16/fp16 rounding:
+    q against K = k_i8 * k_scale, V = v_i8 * v_scale ("implementation A", kvq/int8_ref.py:62-91)."""
+    ks, vs = static["k_scale"], static["v_scale"]
+    _is_cuda(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, ks, vs)
+    if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise RuntimeError("kvq_b200: q/out must be bf16")
+    if q.size(2) != k_cache.size(3) or q.stride(2) != 1 or out.stride(2) != 1:
+        raise RuntimeError("kvq_b200: unsupported shape/layout")
+    for t, n in ((cu_seqlens_q, "cu_seqlens_q"), (seq_lens, "seq_lens"), (block_table, "block_table")):
+        if t.dtype != torch.int32:
+            raise RuntimeError(f"kvq_b200: {n} must be int32")
+    if block_table.stride(1) != 1 or not cu_seqlens_q.is_contiguous() or not seq_lens.is_contiguous():
+        raise RuntimeError("kvq_b200: metadata tensors must be contiguous")
+    _check_scale(ks, "k_scale")
+    _check_scale(vs, "v_scale")
+    num_seqs = cu_seqlens_q.size(0) - 1
+    if num_seqs <= 0 or q.size(0) == 0:
+        return out
+    kc, kc_sb, kc_sn, kc_sh = _cache_args(k_cache)
+    vc, vc_sb, vc_sn, vc_sh = _cache_args(v_cache)
+    pk, pv = _scale_flags(ks, vs)
+    key = q.device.index if q.device.index is not None else torch.cuda.current_device()
+    need = ext().kvq_prefill_workspace_size(num_seqs)
+    ws = _PREFILL_WS.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, ext().kvq_prefill_workspace_size(4096)), dtype=torch.uint8, device=q.device)
+        _PREFILL_WS[key] = ws
+    _native.check(ext().kvq_int8_prefill_attention(
+        q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
+        ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(0), q.size(1), k_cache.size(2), q.size(2),
+        k_cache.size(1), k_cache.size(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1), kc_sb, kc_sn, kc_sh,
+        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, SHORT_Q, ws.data_ptr(), ws.numel(), _stream()))
+    return out
+
+
+def prefill_status(device=None):
+    """Debug: status word of the last prefill_attention call on `device` (0 = clean). Synchronizes the stream."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _PREFILL_WS.get(key)
+    if ws is None:
+        return 0
+    torch.cuda.current_stream().synchronize()
+    return int(ws[:4].view(torch.int32).item())
+
+
 def check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan):
     """KVQ_DEBUG=1: host-side bounds checks of one batch before the kernels run; raises
     RuntimeError("kvq input check: ...") like the reference (kvq/cuda_kernels.py:134-169). Synchronizes, so it
@@ -302,15 +355,41 @@ def check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan):
         raise RuntimeError("kvq input check: " + "; ".join(problems[:8]))
 
 
+def long_path():
+    """Which kernel serves long queries: "int8" (prefill_attention, reads the INT8 pages directly, needs nothing
+    outside this package) or "fa" (dequantize + vLLM's paged FlashAttention, as the reference does). The environment
+    variable KVQ_LONG_PATH picks one; by default "fa" is used where vLLM's kernel can be imported (on B200 it is the
+    faster of the two for large prefills) and "int8" otherwise."""
+    choice = os.environ.get("KVQ_LONG_PATH", "auto")
+    if choice in ("int8", "fa"):
+        return choice
+    if choice != "auto":
+        raise RuntimeError(f"kvq_b200: KVQ_LONG_PATH must be int8, fa or auto, got {choice!r}")
+    global _FA_IMPORTABLE
+    if _FA_IMPORTABLE is None:
+        try:
+            _flash_attn_varlen()
+            _FA_IMPORTABLE = True
+        except Exception:  # noqa: BLE001
+            _FA_IMPORTABLE = False
+    return "fa" if _FA_IMPORTABLE else "int8"
+
+
+_FA_IMPORTABLE = None
+
+
 def paged_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, max_query_len, softmax_scale,
                     static, plan=None, segm=None):
     """Both paths for one batch, as the backend runs them (kvq/cuda_kernels.py:172-183); plan from plan_long,
-    None if every request is short."""
+    None if every request is short. The long requests go to long_attention or prefill_attention (see long_path)."""
     if os.environ.get("KVQ_DEBUG") == "1":
         check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan)
     if plan is not None:
-        long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, max_query_len, plan,
-                       softmax_scale, static)
+        if long_path() == "int8":
+            prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static)
+        else:
+            long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, max_query_len, plan,
+                           softmax_scale, static)
     if plan is None or plan.has_short:
         decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static, segm,
                          max_query_len)

@@ -31,12 +31,13 @@ def run_decode(case, max_query_len=None, out=None, interleaved=False, device_cas
     return out.float().cpu().numpy()
 
 
-def oracle_attention(case, requests=None, short_q=8):
+def oracle_attention(case, requests=None, short_q=8, long_kv_bf16=True):
     st = case["static"]
     return orc.paged_static_attention(case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(),
                                       case["cu_seqlens_q"].numpy(), case["seq_lens"].numpy(),
                                       case["block_table"].numpy(), case["softmax_scale"], st["k_scale"].numpy(),
-                                      st["v_scale"].numpy(), short_q=short_q, p_tile=32, requests=requests)
+                                      st["v_scale"].numpy(), short_q=short_q, p_tile=32, requests=requests,
+                                      long_kv_bf16=long_kv_bf16)
 
 
 def short_row_mask(case, limit=8):

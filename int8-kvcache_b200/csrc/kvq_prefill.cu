@@ -21,6 +21,8 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "kvq_common.cuh"
 #include "kvq_host.h"
 #include "kvq_ptx.cuh"
@@ -133,7 +135,8 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 // plan: m tiles per request (long requests only), exclusive prefix
 // ------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __restrict__ cu_q, int num_seqs, int TQ, int min_q,
-                                                          int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
+                                                          int per_cta, int32_t* __restrict__ hdr,
+                                                          int32_t* __restrict__ prefix) {
   __shared__ int s_warp[8];
   __shared__ int s_carry;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -144,7 +147,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __rest
     int n = 0;
     if (r < num_seqs) {
       const int qlen = cu_q[r + 1] - cu_q[r];
-      n = qlen > min_q ? (qlen + TQ - 1) / TQ : 0;
+      n = qlen > min_q ? ((qlen + TQ - 1) / TQ + per_cta - 1) / per_cta : 0;
     }
     int incl = n;
 #pragma unroll
@@ -514,6 +517,453 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
 }
 
 // ------------------------------------------------------------------------------------------------------
+// warp-specialized variant: two m tiles per CTA share one K/V stream
+// ------------------------------------------------------------------------------------------------------
+// 13 warps: warps 0-3 and 4-7 are the softmax groups of m tile 0 and 1 (one thread per row), warps 8-11 widen the
+// int8 K/V boxes into fp16 operand tiles and issue the TMA loads, warp 12 (one lane) issues every tcgen05.mma.
+// The groups meet only through mbarriers, so S = Q.K^T of step j + 1 runs on the tensor core while the softmax
+// groups work on step j, and O += P.V of step j starts the moment a group has written its P.
+//   TMEM: S[tile][step & 1] 4 x 64 columns, O[tile] 2 x D columns.
+//   smem: Q 2 tiles, fp16 K and V 2 stages each, P 2 buffers per tile, int8 landing zones 2 stages each.
+constexpr int WS_THREADS = 13 * 32;
+#ifdef KVQ_PF_TIMELINE
+__device__ long long g_pf_timeline[3 * 64 * 8];   // [role][step][event]
+#define PF_TL(role, step, ev)                                                                      \
+  do {                                                                                             \
+    if (blockIdx.x == gridDim.x / 2 && (step) < 64) g_pf_timeline[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
+  } while (0)
+#else
+#define PF_TL(role, step, ev) do { } while (0)
+#endif
+constexpr int WS_TMEM_COLS = 512;
+enum WsBar {
+  WB_STGK = 0,       // [2] int8 K boxes landed (TMA)
+  WB_STGV = 2,       // [2]
+  WB_KF_READY = 4,   // [2] fp16 K tile written (128 converter threads)
+  WB_VF_READY = 6,   // [2]
+  WB_KF_FREE = 8,    // [2] tensor core done with the fp16 K tile (commit)
+  WB_VF_FREE = 10,   // [2]
+  WB_S_READY = 12,   // [tile * 2 + buffer] S computed (commit)
+  WB_S_FREE = 16,    // [tile * 2 + buffer] S read into registers (128 softmax threads)
+  WB_P_READY = 20,   // [tile * 2 + buffer] P written (128 softmax threads)
+  WB_O_DONE = 24,    // [tile * 2 + (step & 1)] O += P.V of that step finished (commit)
+  WB_Q_READY = 28,   // q tiles written (256 softmax threads)
+  WB_STGK_FREE = 29, // [2] landing zone read by every converter (128 threads)
+  WB_STGV_FREE = 31, // [2]
+  WB_COUNT = 33
+};
+
+template <int D>
+struct WsGeom {
+  static constexpr int NSLAB = D / 64;
+  static constexpr int Q_TILE = NSLAB * PF_BM * 128;
+  static constexpr int KV_SLAB = PF_BN * 128;
+  static constexpr int KV_TILE = NSLAB * KV_SLAB;
+  static constexpr int P_TILE = PF_BM * 128;
+  static constexpr int STG = PF_BN * D;
+  static constexpr int OFF_Q = 0, OFF_K = OFF_Q + 2 * Q_TILE, OFF_V = OFF_K + 2 * KV_TILE, OFF_P = OFF_V + 2 * KV_TILE,
+                       OFF_SK = OFF_P + 4 * P_TILE, OFF_SV = OFF_SK + 2 * STG, END = OFF_SV + 2 * STG;
+  static constexpr int SMEM = 1024 + END;
+};
+
+// Bounded wait that also gives up as soon as any thread of the CTA has given up. Called by converged warps; the
+// result is uniform over the warp, so the warp-collective tensor-memory instructions that follow stay converged.
+__device__ __forceinline__ bool ws_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag);
+__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, ws_wait_thread(bar, parity, abort_flag));
+}
+__device__ __forceinline__ bool ws_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > (1ll << 31)) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(WS_THREADS, 1)
+    prefill_ws_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
+  using Gm = WsGeom<D>;
+  constexpr int NSLAB = Gm::NSLAB;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t s_bar[WB_COUNT];
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_req;
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_wait();   // the plan below is written by prefill_plan_kernel
+  const int total = a.hdr[1];   // pairs of m tiles
+  const int pix = blockIdx.x / a.Hkv, kvh = blockIdx.x - pix * a.Hkv;
+  if (pix >= total) return;
+  const int pair = total - 1 - pix;   // later m tiles of a request see more keys: start them first
+
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* p_base = smem_raw + (base - smem_u32(smem_raw));
+  auto bar = [&](int i) { return smem_u32(&s_bar[i]); };
+
+  if (warp == 12) tmem_alloc(smem_u32(&s_tmem), WS_TMEM_COLS);
+  if (tid == 0) {
+    s_abort = 0;
+    for (int i = 0; i < WB_COUNT; ++i) {
+      const int n = (i >= WB_KF_READY && i < WB_KF_FREE) || (i >= WB_S_FREE && i < WB_O_DONE) || i >= WB_STGK_FREE
+                        ? 128
+                        : (i == WB_Q_READY ? 256 : 1);
+      mbar_init(bar(i), n);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int r = tid; r < a.num_seqs; r += WS_THREADS)
+    if (a.prefix[r] <= pair && pair < a.prefix[r + 1]) s_req = r;
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem;
+  volatile int* abort_flag = &s_abort;
+
+  const int req = s_req, mt0 = 2 * (pair - a.prefix[req]);
+  const int tok0 = a.cu_q[req], qlen = a.cu_q[req + 1] - tok0, L = a.seq_lens[req];
+  const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
+  // key steps of each m tile: tile t covers query tokens [t_first, t_last]; keys [0, L - qlen + 1 + t_last) are visible
+  auto steps_of = [&](int mt) {
+    const int t_first = mt * a.TQ;
+    if (t_first >= qlen) return 0;
+    const int kmax = L - qlen + 1 + min(qlen, t_first + a.TQ) - 1;
+    return kmax > 0 ? (kmax + PF_BN - 1) / PF_BN : 0;
+  };
+  const int nk0 = steps_of(mt0), nk1 = steps_of(mt0 + 1), nk = max(nk0, nk1);
+  constexpr uint32_t ID_S = instr_desc(PF_BM, PF_BN, false), ID_O = instr_desc(PF_BM, D, true);
+
+  if (warp < 8) {
+    // ================= softmax group of m tile t =================
+    const int t = warp >> 2, row = tid & 127, mt = mt0 + t, nkt = t ? nk1 : nk0;
+    uint8_t* p_q = p_base + Gm::OFF_Q + t * Gm::Q_TILE;
+    uint8_t* p_p = p_base + Gm::OFF_P + t * 2 * Gm::P_TILE;   // two buffers, by step parity
+    const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t t_s = tmem + t * 2 * PF_BN + t_lane, t_o = tmem + 4 * PF_BN + t * D + t_lane;
+    const int tl = row / a.G, hg = row - tl * a.G, tq = mt * a.TQ + tl;
+    const bool valid = tl < a.TQ && tq < qlen;
+    const int lim = valid ? L - qlen + 1 + tq : 0x7fffffff;   // padding rows hold q = 0 and are never stored
+    float c_row = 0.f;
+    {
+      const __nv_bfloat16* qrow = a.q + static_cast<int64_t>(tok0 + tq) * a.q_st + static_cast<int64_t>(kvh * a.G + hg) * a.q_sh;
+      const float* ksr = a.ks + kvh * (a.pc_k ? D : 1);
+      auto scaled = [&](int c, float (&f)[8]) {   // channels 8c..8c+7 of q * s_k
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[2 * e] = bf16lo(ww[e]), f[2 * e + 1] = bf16hi(ww[e]);
+        if (a.pc_k) {
+          const float4 s0 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c), s1 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c + 1);
+          f[0] *= s0.x, f[1] *= s0.y, f[2] *= s0.z, f[3] *= s0.w, f[4] *= s1.x, f[5] *= s1.y, f[6] *= s1.z, f[7] *= s1.w;
+        }
+      };
+      float amax = 0.f;
+      if (valid) {
+#pragma unroll 4
+        for (int c = 0; c < D / 8; ++c) {
+          float f[8];
+          scaled(c, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
+        }
+      }
+      // power-of-two row scale that puts the largest |q * s_k| into [2^14, 2^15): fp16 keeps 11 significant bits
+      int ex = 0;
+      if (amax > 0.f) frexpf(amax, &ex);
+      const int sh = amax > 0.f ? max(-60, min(60, 15 - ex)) : 0;
+      const float up = ldexpf(1.f, sh);
+      c_row = a.scale_log2 * ldexpf(1.f, -sh) * (a.pc_k ? 1.f : __ldg(ksr));
+#pragma unroll 2
+      for (int c = 0; c < D / 8; ++c) {
+        uint4 o = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) {
+          float f[8];
+          scaled(c, f);
+          o = make_uint4(pack_f16x2(f[0] * up, f[1] * up), pack_f16x2(f[2] * up, f[3] * up), pack_f16x2(f[4] * up, f[5] * up),
+                         pack_f16x2(f[6] * up, f[7] * up));
+        }
+        *reinterpret_cast<uint4*>(p_q + (c >> 3) * (PF_BM * 128) + slab_off(row, c & 7)) = o;
+      }
+    }
+    fence_proxy_async();
+    mbar_arrive(bar(WB_Q_READY));
+
+    float m_ref = -1e30f, l_sum = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkt && ok; ++j) {
+      const int b = j & 1;
+      if (tid == 0) PF_TL(0, j, 0);
+      ok = ws_wait(bar(WB_S_READY + t * 2 + b), (j >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (tid == 0) PF_TL(0, j, 1);
+      tc_fence_after();
+      uint32_t sr[PF_BN];
+      {
+        uint32_t lo[32], hi[32];
+        tmem_ld32(t_s + b * PF_BN, lo);
+        tmem_ld32(t_s + b * PF_BN + 32, hi);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sr[i] = lo[i], sr[32 + i] = hi[i];
+      }
+      tc_fence_before();
+      if (tid == 0) PF_TL(0, j, 2);
+      mbar_arrive(bar(WB_S_FREE + t * 2 + b));
+      if (tid == 0) PF_TL(0, j, 3);
+      const int n_base = j * PF_BN;
+      float mx = -INFINITY;
+      if (n_base + PF_BN <= lim) {
+#pragma unroll
+        for (int i = 0; i < PF_BN; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < PF_BN; ++i) {
+          if (n_base + i >= lim) sr[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
+          mx = fmaxf(mx, __uint_as_float(sr[i]));
+        }
+      }
+      const float tile_max = mx * c_row;   // c_row > 0
+      const bool grow = tile_max > m_ref + 8.f;
+      float alpha = 1.f;
+      if (grow) {
+        alpha = ex2(m_ref - tile_max);   // 0 on the first step (m_ref = -1e30)
+        m_ref = tile_max;
+        l_sum *= alpha;
+      }
+      if (tid == 0) PF_TL(0, j, 4);
+      if (j >= 2) {   // P.V of step j - 2 has finished reading this step's P buffer
+        ok = ws_wait(bar(WB_O_DONE + t * 2 + b), ((j - 2) >> 1) & 1, abort_flag);
+        if (!ok) break;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {   // rescale O (rare after the first steps): P.V of step j - 1 first
+        ok = ws_wait(bar(WB_O_DONE + t * 2 + (b ^ 1)), ((j - 1) >> 1) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            uint32_t o[32];
+            tmem_ld32(t_o + c, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(t_o + c, o);
+          }
+          tmem_wait_st();
+        }
+      }
+      if (tid == 0) PF_TL(0, j, 5);
+      {
+        const float nm = -m_ref;
+        float ls = 0.f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float p0 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e]), c_row, nm));
+            const float p1 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e + 1]), c_row, nm));
+            ls += p0 + p1;
+            w[e] = pack_f16x2(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(p_p + b * Gm::P_TILE + slab_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l_sum += ls;
+      }
+      if (tid == 0) PF_TL(0, j, 6);
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(bar(WB_P_READY + t * 2 + b));
+      if (tid == 0) PF_TL(0, j, 7);
+    }
+    // ---- epilogue: O / denominator * s_v -> bf16 ----
+    if (ok && nkt > 0) ok = ws_wait(bar(WB_O_DONE + t * 2 + ((nkt - 1) & 1)), ((nkt - 1) >> 1) & 1, abort_flag);
+    if (ok && nkt > 0) {
+      tc_fence_after();
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(tok0 + tq) * a.o_st + static_cast<int64_t>(kvh * a.G + hg) * a.o_sh;
+      const float inv = 1.f / fmaxf(l_sum, 1e-30f);
+      const float* vsr = a.vs + kvh * (a.pc_v ? D : 1);
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld32(t_o + c, o);
+        tmem_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            float sv[8];
+            if (a.pc_v) {
+              const float4 s0 = __ldg(reinterpret_cast<const float4*>(vsr + c + i)), s1 = __ldg(reinterpret_cast<const float4*>(vsr + c + i + 4));
+              sv[0] = s0.x, sv[1] = s0.y, sv[2] = s0.z, sv[3] = s0.w, sv[4] = s1.x, sv[5] = s1.y, sv[6] = s1.z, sv[7] = s1.w;
+            } else {
+              const float one = __ldg(vsr);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) sv[e] = one;
+            }
+            uint32_t w[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+              w[e] = pack_bf16x2(__uint_as_float(o[i + 2 * e]) * inv * sv[2 * e], __uint_as_float(o[i + 2 * e + 1]) * inv * sv[2 * e + 1]);
+            *reinterpret_cast<uint4*>(orow + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    } else if (valid && nkt == 0) {   // no visible key (seq_len < q_len): defined output
+      __nv_bfloat16* orow = a.out + static_cast<int64_t>(tok0 + tq) * a.o_st + static_cast<int64_t>(kvh * a.G + hg) * a.o_sh;
+      for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  } else if (warp < 12) {
+    // ================= converters: TMA issue + int8 -> fp16 =================
+    const int ctid = tid - 256;
+    const bool issuer = warp == 8;
+    auto key_of = [&](int j) {   // first key of this lane's 16-key box of step j; boxes past the end re-read the first
+      const int n0 = j * PF_BN, n = n0 + 16 * lane;
+      return n < L ? n : n0;
+    };
+    auto issue = [&](bool is_k, int j, int page) {   // warp 8: lane i < 4 loads the i-th box
+      const uint32_t full = bar((is_k ? WB_STGK : WB_STGV) + (j & 1));
+      if (lane == 0) mbar_expect_tx(full, Gm::STG);
+      __syncwarp();
+      if (lane < 4) {
+        const int off = key_of(j) & a.bs_mask;
+        const int* pos = is_k ? a.kpos : a.vpos;
+        auto coord = [&](int s) { return pos[0] == s ? off : (pos[1] == s ? kvh : page); };
+        tma_load_4d(base + (is_k ? Gm::OFF_SK : Gm::OFF_SV) + (j & 1) * Gm::STG + lane * 16 * D, is_k ? &tm_k : &tm_v, 0,
+                    coord(1), coord(2), coord(3), full);
+      }
+    };
+    int pg_a = 0, pg_b = 0;   // page ids (lanes 0-3 of warp 8) of the next two steps to issue
+    if (issuer) {
+      if (lane < 4) {
+        if (nk > 0) pg_a = bt[key_of(0) >> a.lbs];
+        if (nk > 1) pg_b = bt[key_of(1) >> a.lbs];
+      }
+      if (nk > 0) issue(true, 0, pg_a), issue(false, 0, pg_a);
+      if (nk > 1) issue(true, 1, pg_b), issue(false, 1, pg_b);
+      pg_a = 0, pg_b = 0;
+      if (lane < 4) {
+        if (nk > 2) pg_a = bt[key_of(2) >> a.lbs];
+        if (nk > 3) pg_b = bt[key_of(3) >> a.lbs];
+      }
+    }
+    bool ok = true;
+    for (int j = 0; j < nk && ok; ++j) {
+      const int s = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      // pg_a belongs to step j + 2 (issued below), pg_b to step j + 3
+      if (ctid == 0) PF_TL(1, j, 0);
+      ok = ws_wait(bar(WB_STGK + s), ph, abort_flag);
+      if (ctid == 0) PF_TL(1, j, 1);
+      if (ok && j >= 2) ok = ws_wait(bar(WB_KF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (ctid == 0) PF_TL(1, j, 2);
+      widen_tile<D>(p_base + Gm::OFF_SK + s * Gm::STG, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
+      fence_proxy_async();
+      mbar_arrive(bar(WB_KF_READY + s));
+      mbar_arrive(bar(WB_STGK_FREE + s));
+      if (ctid == 0) PF_TL(1, j, 3);
+      if (issuer && j + 2 < nk) {   // every converter has left the landing zone before it is refilled
+        ok = ws_wait(bar(WB_STGK_FREE + s), ph, abort_flag);
+        if (ok) issue(true, j + 2, pg_a);
+      }
+      if (ctid == 0) PF_TL(1, j, 4);
+      ok = ws_wait(bar(WB_STGV + s), ph, abort_flag);
+      if (ctid == 0) PF_TL(1, j, 5);
+      if (ok && j >= 2) ok = ws_wait(bar(WB_VF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (ctid == 0) PF_TL(1, j, 6);
+      widen_tile<D>(p_base + Gm::OFF_SV + s * Gm::STG, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
+      fence_proxy_async();
+      mbar_arrive(bar(WB_VF_READY + s));
+      mbar_arrive(bar(WB_STGV_FREE + s));
+      if (ctid == 0) PF_TL(1, j, 7);
+      if (issuer) {
+        if (j + 2 < nk) {
+          ok = ok && ws_wait(bar(WB_STGV_FREE + s), ph, abort_flag);
+          if (ok) issue(false, j + 2, pg_a);
+        }
+        pg_a = pg_b;
+        pg_b = (lane < 4 && j + 4 < nk) ? bt[key_of(j + 4) >> a.lbs] : 0;
+      }
+    }
+  } else if (lane == 0) {
+    // ================= tensor-core issue (one thread) =================
+    bool ok = ws_wait_thread(bar(WB_Q_READY), 0, abort_flag);
+    // Descriptors differ only in their 14-bit start-address field (address >> 4): one base per operand, the
+    // tile / slab / k-step offsets (compile-time constants once the loops are unrolled) are added to it.
+    const uint64_t d_q = smem_desc(base + Gm::OFF_Q, 16, 1024), d_k = smem_desc(base + Gm::OFF_K, 16, 1024),
+                   d_p = smem_desc(base + Gm::OFF_P, 16, 1024), d_v = smem_desc(base + Gm::OFF_V, Gm::KV_SLAB, 1024);
+    auto issue_qk = [&](int j) {
+      const int s = j & 1;
+      ok = ok && ws_wait_thread(bar(WB_KF_READY + s), (j >> 1) & 1, abort_flag);
+      const uint64_t d_ks = d_k + static_cast<uint64_t>((s * Gm::KV_TILE) >> 4);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (!ok || j >= (t ? nk1 : nk0)) continue;
+        if (j >= 2) ok = ws_wait_thread(bar(WB_S_FREE + t * 2 + s), ((j - 2) >> 1) & 1, abort_flag);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint32_t d_s = tmem + (t * 2 + s) * PF_BN;
+#pragma unroll
+        for (int sl = 0; sl < NSLAB; ++sl)
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16(d_s, d_q + static_cast<uint64_t>((t * Gm::Q_TILE + sl * (PF_BM * 128) + ks * 32) >> 4),
+                     d_ks + static_cast<uint64_t>((sl * Gm::KV_SLAB + ks * 32) >> 4), ID_S, (sl | ks) ? 1u : 0u);
+        umma_commit(bar(WB_S_READY + t * 2 + s));
+      }
+      if (ok) umma_commit(bar(WB_KF_FREE + s));
+    };
+    if (ok && nk > 0) issue_qk(0);
+    for (int j = 0; j < nk && ok; ++j) {
+      const int s = j & 1;
+      PF_TL(2, j, 0);
+      if (j + 1 < nk) issue_qk(j + 1);
+      PF_TL(2, j, 1);
+      ok = ok && ws_wait_thread(bar(WB_VF_READY + s), (j >> 1) & 1, abort_flag);
+      PF_TL(2, j, 2);
+      const uint64_t d_vs = d_v + static_cast<uint64_t>((s * Gm::KV_TILE) >> 4);
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        if (!ok || j >= (t ? nk1 : nk0)) continue;
+        ok = ws_wait_thread(bar(WB_P_READY + t * 2 + s), (j >> 1) & 1, abort_flag);
+        if (!ok) continue;
+        tc_fence_after();
+        const uint64_t d_ps = d_p + static_cast<uint64_t>(((t * 2 + s) * Gm::P_TILE) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16(tmem + 4 * PF_BN + t * D, d_ps + static_cast<uint64_t>((ks * 32) >> 4),
+                   d_vs + static_cast<uint64_t>((ks * 16 * 128) >> 4), ID_O, (j | ks) ? 1u : 0u);
+        umma_commit(bar(WB_O_DONE + t * 2 + s));
+        PF_TL(2, j, 3 + t);
+      }
+      if (ok) umma_commit(bar(WB_VF_FREE + s));
+    }
+  }
+
+  // ---- common exit ----
+  if (*abort_flag) {
+    // A bounded wait expired somewhere in the CTA: report it and give copies and tensor-core work still in flight
+    // a bounded time to land before shared and tensor memory are released.
+    if (tid == 0) atomicExch(a.hdr, 1);
+    const long long t0 = clock64();
+    while (clock64() - t0 < (1ll << 20)) __nanosleep(256);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 12) tmem_dealloc(tmem, WS_TMEM_COLS);
+}
+
+// ------------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------------
 size_t pf_align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -577,6 +1027,8 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_prefill_attention
   if (dev >= 0 && dev < 64 && !g_pf_ready[dev]) {
     KVQ_CUDA(cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeom<64>::SMEM));
     KVQ_CUDA(cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeom<128>::SMEM));
+    KVQ_CUDA(cudaFuncSetAttribute(prefill_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<64>::SMEM));
+    KVQ_CUDA(cudaFuncSetAttribute(prefill_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<128>::SMEM));
     g_pf_ready[dev] = true;
   }
 
@@ -600,15 +1052,34 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_prefill_attention
                                     vc_stride_h, 1, &tm_v, a.vpos)) != KVQ_OK)
     return rc;
 
-  prefill_plan_kernel<<<1, 256, 0, s>>>(cu_q, num_seqs, a.TQ, a.min_q, a.hdr, a.prefix);
+  // KVQ_PREFILL_SIMPLE=1 selects the one-m-tile-per-CTA kernel without warp specialization (debugging aid)
+  static const bool simple = [] {
+    const char* e = getenv("KVQ_PREFILL_SIMPLE");
+    return e && e[0] == '1';
+  }();
+  const int per_cta = simple ? 1 : 2;
+  prefill_plan_kernel<<<1, 256, 0, s>>>(cu_q, num_seqs, a.TQ, a.min_q, per_cta, a.hdr, a.prefix);
   KVQ_CUDA(cudaGetLastError());
-  // upper bound of the m tiles: sum over requests of ceil(q_len / TQ) <= tokens / TQ + requests
-  const int64_t max_tiles = total_query_tokens / a.TQ + num_seqs;
-  KVQ_REQUIRE(max_tiles * num_kv_heads < (1ll << 31), "prefill_attention: batch too large");
-  const dim3 grid(static_cast<unsigned>(max_tiles * num_kv_heads));
-  if (head_dim == 128)
-    KVQ_CUDA(pf_launch_pdl(prefill_kernel<128>, grid, dim3(PF_THREADS), PfGeom<128>::SMEM, s, a, tm_k, tm_v));
-  else
-    KVQ_CUDA(pf_launch_pdl(prefill_kernel<64>, grid, dim3(PF_THREADS), PfGeom<64>::SMEM, s, a, tm_k, tm_v));
+  // upper bound of the work items: sum over requests of ceil(m tiles / per_cta), m tiles = ceil(q_len / TQ)
+  const int64_t max_items = total_query_tokens / (static_cast<int64_t>(a.TQ) * per_cta) + num_seqs;
+  KVQ_REQUIRE(max_items * num_kv_heads < (1ll << 31), "prefill_attention: batch too large");
+  const dim3 grid(static_cast<unsigned>(max_items * num_kv_heads));
+  if (simple) {
+    if (head_dim == 128)
+      KVQ_CUDA(pf_launch_pdl(prefill_kernel<128>, grid, dim3(PF_THREADS), PfGeom<128>::SMEM, s, a, tm_k, tm_v));
+    else
+      KVQ_CUDA(pf_launch_pdl(prefill_kernel<64>, grid, dim3(PF_THREADS), PfGeom<64>::SMEM, s, a, tm_k, tm_v));
+  } else {
+    if (head_dim == 128)
+      KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<128>, grid, dim3(WS_THREADS), WsGeom<128>::SMEM, s, a, tm_k, tm_v));
+    else
+      KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<64>, grid, dim3(WS_THREADS), WsGeom<64>::SMEM, s, a, tm_k, tm_v));
+  }
   return KVQ_OK;
 }
+
+#ifdef KVQ_PF_TIMELINE
+extern "C" __attribute__((visibility("default"))) int kvq_debug_pf_timeline(long long* host, int n) {
+  return cudaMemcpyFromSymbol(host, g_pf_timeline, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
+}
+#endif

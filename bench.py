@@ -411,6 +411,62 @@ def run_suite(args):
                    note="KV bytes counted once although 4 m tiles (56 rows) use them; average over the copies")
 
 
+def run_prefill_suite(args):
+    """Long-query attention (more than SHORT_Q query tokens per request) on the INT8 cache, both routes: the
+    INT8-page tensor-core kernel (prefill_attention) and the reference's route (dequantize pages to a temporary
+    bf16 cache + vLLM's paged FlashAttention, a library kernel). Tensor-bound: TFLOP/s = 4 * rows * visible keys
+    * head_dim / time, against the measured dense bf16 peak. K/V (>= 130 MB per case except the smallest) are read
+    through L2 many times by design, so no L2 flush applies."""
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    from kvq_b200 import cuda_kernels as ck
+    from kvq_b200 import workloads
+
+    try:
+        peak_tf = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]
+        peak_src = "measured"
+    except Exception:  # noqa: BLE001
+        peak_tf, peak_src = 1590.0, "fallback"
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return float(np.median(ts))
+
+    for batch, q_len, ctx in ((16, 64, 4096), (32, 512, 512), (8, 4096, 4096), (4, 2048, 8192), (1, 16384, 16384)):
+        c = workloads.decode_batch_on_device(batch, ctx, dev, seed=1005, q_len=q_len)
+        q, cu, sl, bt, st = c["q"], c["cu_seqlens_q"], c["seq_lens"], c["block_table"], c["static"]
+        out = torch.zeros_like(q)
+        flops = 4.0 * batch * HQ * D * (q_len * (ctx - q_len) + q_len * (q_len + 1) / 2)
+        ms = timed(lambda: ck.prefill_attention(q, c["kq"], c["vq"], out, cu, sl, bt, c["softmax_scale"], st))
+        assert ck.prefill_status() == 0
+        line = {"suite": "prefill", "workload": f"{batch} requests x {q_len} query tokens, context {ctx}",
+                "kernel": "prefill_ws_kernel (INT8 pages, tcgen05)", "ms": round(ms, 4),
+                "TFLOPs": round(flops / ms / 1e9, 1), "frac_of_bf16_peak": round(flops / ms / 1e9 / peak_tf, 3),
+                "peak": f"{peak_tf} TFLOP/s dense bf16 ({peak_src})", "timing": "CUDA events, median of 10 calls after 3 warm-ups"}
+        try:
+            plan = ck.plan_long(cu.cpu(), sl.cpu(), BLOCK)
+            out2 = torch.zeros_like(q)
+            ms2 = timed(lambda: ck.long_attention(q, c["kq"], c["vq"], out2, cu, sl, bt, q_len, plan, c["softmax_scale"], st))
+            line["dequant_plus_flash_attention_ms"] = round(ms2, 4)
+            line["dequant_plus_flash_attention_TFLOPs"] = round(flops / ms2 / 1e9, 1)
+            line["rel_l2_between_routes"] = round(float((out.float() - out2.float()).norm() / out2.float().norm()), 5)
+        except Exception as e:  # noqa: BLE001  (vLLM's kernel is optional)
+            line["dequant_plus_flash_attention_ms"] = None
+            line["flash_attention_unavailable"] = str(e)[:120]
+        print(json.dumps(line), flush=True)
+        del c, q, out
+
+
 # --------------------------------------------------------------------------------------------------------
 # --workload model_step: full decode step of a Qwen2.5-7B-geometry decoder (a caller of the hot path)
 # --------------------------------------------------------------------------------------------------------
@@ -477,7 +533,8 @@ def main():
                     help="model_step: full 28-layer decode step (512 requests x 6144 context over all GPUs)")
     ap.add_argument("--model-requests", type=int, default=512)
     ap.add_argument("--model-ctx", type=int, default=6144)
-    ap.add_argument("--suite", default=None, choices=["kernels"], help="extra per-kernel lines instead of the headline")
+    ap.add_argument("--suite", default=None, choices=["kernels", "prefill"],
+                    help="extra per-kernel lines instead of the headline (prefill: long-query attention, both routes)")
     ap.add_argument("--q-len", type=int, default=1, help="query tokens per request (profile runs; headline is 1)")
     ap.add_argument("--ctx-min", type=int, default=0, help="draw contexts uniformly from [ctx-min, ctx] (profile runs)")
     ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
@@ -497,6 +554,9 @@ def main():
         return
     if args.suite == "kernels":
         run_suite(args)
+        return
+    if args.suite == "prefill":
+        run_prefill_suite(args)
         return
     run_ours(args, rank, world, local_rank)
 

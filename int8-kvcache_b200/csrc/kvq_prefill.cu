@@ -2,26 +2,24 @@
 //
 // The reference serves requests with more than SHORT_Q query tokens by dequantizing their pages into a temporary
 // bf16 paged cache and running FlashAttention over it (kvq/cuda_kernels.py:61-131, "implementation A" of
-// kvq/int8_ref.py:62-91); its authors list the per-layer copy as the path's main cost (docs/WALKTHROUGH.md:408-409).
-// This kernel computes the same attention - bf16 q against K = k_i8 * s_k and V = v_i8 * s_v - without the copy:
+// kvq/int8_ref.py:62-91). This kernel computes the same attention - bf16 q against K = k_i8 * s_k and
+// V = v_i8 * s_v - from the int8 pages, without the temporary cache (and without its bf16 rounding of K and V):
 //
-//   prefill_plan_kernel   m tiles per long request, exclusive prefix (one block)
-//   prefill_kernel        one CTA per (request, kv head, m tile of 128 (token, q head) rows); 128 threads, one per row
+//   prefill_plan_kernel   work items (pairs of m tiles) per long request, exclusive prefix (one block)
+//   prefill_ws_kernel     one CTA per (request, kv head, pair of m tiles of 128 (token, q head) rows)
 //
-// Per CTA: q rows are loaded once, multiplied by s_k[channel] (exact fold: q.(k_i8 * s_k) = (q * s_k).k_i8),
-// scaled by a per-row power of two into fp16 range and kept in shared memory as the A operand. K/V arrive as int8
-// 16-key boxes by TMA (cp.async.bulk.tensor, mbarrier completion), are widened to fp16 (exact: |k_i8| <= 127)
-// into 128-byte-swizzled operand tiles, and both products run on the 5th-generation tensor cores:
-//   S[128 x 64]   = Q . K^T    tcgen05.mma kind::f16, A and B K-major from shared memory, fp32 accumulator in TMEM
-//   O[128 x D]   += P . V      P fp16 from shared memory (K-major), V MN-major (its natural [key][channel] layout)
-// Each thread reads its own row of S from TMEM (tcgen05.ld), does the online softmax in fp32 with the running
-// maximum held back until it grows by more than 2^8 (the accumulator in TMEM is rescaled only then), and writes
-// its P row. s_v and 1 / denominator are applied once in the epilogue. All waits are bounded; a wait that expires
-// sets the status word in the workspace and the CTA leaves after releasing its tensor memory.
+// q rows are loaded once, multiplied by s_k[channel] (exact fold: q.(k_i8 * s_k) = (q * s_k).k_i8), scaled by a
+// per-row power of two into fp16 range and kept in shared memory as the A operand. K/V arrive as int8 16-key boxes
+// by TMA (cp.async.bulk.tensor, mbarrier completion), are widened to fp16 (exact: |k_i8| <= 127) into
+// 128-byte-swizzled operand tiles, and both products run on the 5th-generation tensor cores:
+//   S[128 x 128]  = Q . K^T    tcgen05.mma kind::f16, A and B K-major from shared memory, fp32 accumulator in TMEM
+//   O[128 x D]   += P . V      P fp16 from tensor memory, V MN-major (its natural [key][channel] layout) from smem
+// Each softmax thread reads its own row of S from TMEM (tcgen05.ld), does the online softmax in fp32 with the
+// running maximum held back until it grows by more than 2^8 (the accumulator in TMEM is rescaled only then), and
+// writes its P row back to TMEM. s_v and 1 / denominator are applied once in the epilogue. All waits are bounded;
+// a wait that expires sets the status word in the workspace and the CTA leaves after releasing its tensor memory.
 #include <cuda.h>
 #include <cuda_fp16.h>
-
-#include <cstdlib>
 
 #include "kvq_common.cuh"
 #include "kvq_host.h"
@@ -30,11 +28,8 @@
 namespace kvq {
 namespace {
 
-constexpr int PF_BM = 128;        // rows per CTA: (query token, q head of the kv head's group), one thread each
-constexpr int PF_BN = 64;         // keys per step
-constexpr int PF_THREADS = 128;
-constexpr int PF_TMEM_COLS = 256;  // S: columns [0, 64), O: columns [64, 64 + D)
-constexpr int PF_HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total m tiles
+constexpr int PF_BM = 128;         // rows per m tile: (query token, q head of the kv head's group), one thread each
+constexpr int PF_HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] work items (pairs of m tiles)
 
 struct PrefillArgs {
   const __nv_bfloat16* q;
@@ -168,364 +163,21 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __rest
 }
 
 // ------------------------------------------------------------------------------------------------------
-// attention
-// ------------------------------------------------------------------------------------------------------
-template <int D>
-struct PfGeom {
-  static constexpr int NSLAB = D / 64;                 // 64-channel slabs per operand tile
-  static constexpr int Q_BYTES = NSLAB * PF_BM * 128;  // fp16 A operand of S = Q.K^T
-  static constexpr int KV_SLAB = PF_BN * 128;          // one [64 keys][64 channels] fp16 slab
-  static constexpr int KV_BYTES = NSLAB * KV_SLAB;
-  static constexpr int P_BYTES = PF_BM * 128;          // [128 rows][64 keys] fp16
-  static constexpr int STG_BYTES = PF_BN * D;          // int8 landing zone of one K or V step (four 16-key boxes)
-  static constexpr int SMEM = 1024 + Q_BYTES + 2 * KV_BYTES + P_BYTES + 2 * STG_BYTES;
-};
-
-// int8 landing zone (TMA boxes of [16 keys][D bytes], hardware-swizzled) -> fp16 operand slabs. 16 channels per item.
-template <int D>
-__device__ __forceinline__ void widen_tile(const uint8_t* stg, uint8_t* dst, int tid) {
-  constexpr int CPR = D / 16;   // 16-byte chunks per key row
-#pragma unroll
-  for (int i = 0; i < PF_BN * CPR / PF_THREADS; ++i) {
-    const int idx = tid + PF_THREADS * i, key = idx / CPR, c = idx - key * CPR, kk = key & 15;
-    const uint32_t src = (key >> 4) * 16 * D + kk * D + ((D == 128 ? (c ^ (kk & 7)) : (c ^ ((kk >> 1) & 3))) << 4);
-    const uint4 w = *reinterpret_cast<const uint4*>(stg + src);
-    uint4 lo, hi;
-    i8x4_to_f16x4(w.x, lo.x, lo.y);
-    i8x4_to_f16x4(w.y, lo.z, lo.w);
-    i8x4_to_f16x4(w.z, hi.x, hi.y);
-    i8x4_to_f16x4(w.w, hi.z, hi.w);
-    uint8_t* slab = dst + (c >> 2) * PfGeom<D>::KV_SLAB;
-    *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2)) = lo;
-    *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2 + 1)) = hi;
-  }
-}
-
-template <int D>
-__global__ void __launch_bounds__(PF_THREADS, 2)
-    prefill_kernel(const PrefillArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
-  using Gm = PfGeom<D>;
-  constexpr int NSLAB = Gm::NSLAB;
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t s_bar[4];   // K landed, V landed, S = Q.K^T done, O += P.V done
-  __shared__ uint32_t s_tmem;
-  __shared__ int s_req;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  pdl_wait();   // the plan below is written by prefill_plan_kernel
-  const int total = a.hdr[1];
-  const int tix = blockIdx.x / a.Hkv, kvh = blockIdx.x - tix * a.Hkv;
-  if (tix >= total) return;
-  const int tile = total - 1 - tix;   // later m tiles of a request see more keys: start them first
-
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* p_base = smem_raw + (base - smem_u32(smem_raw));
-  uint8_t* p_q = p_base;
-  uint8_t* p_k = p_q + Gm::Q_BYTES;
-  uint8_t* p_v = p_k + Gm::KV_BYTES;
-  uint8_t* p_p = p_v + Gm::KV_BYTES;
-  uint8_t* p_sk = p_p + Gm::P_BYTES;
-  uint8_t* p_sv = p_sk + Gm::STG_BYTES;
-  const uint32_t u_q = base, u_k = u_q + Gm::Q_BYTES, u_v = u_k + Gm::KV_BYTES, u_p = u_v + Gm::KV_BYTES,
-                 u_sk = u_p + Gm::P_BYTES, u_sv = u_sk + Gm::STG_BYTES;
-  const uint32_t bar_k = smem_u32(&s_bar[0]), bar_v = smem_u32(&s_bar[1]), bar_s = smem_u32(&s_bar[2]),
-                 bar_o = smem_u32(&s_bar[3]);
-
-  if (warp == 0) tmem_alloc(smem_u32(&s_tmem), PF_TMEM_COLS);
-  if (tid == 0) {
-    for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&s_bar[i]), 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  for (int r = tid; r < a.num_seqs; r += PF_THREADS)
-    if (a.prefix[r] <= tile && tile < a.prefix[r + 1]) s_req = r;
-  fence_proxy_async();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = s_tmem, t_s = tmem, t_o = tmem + PF_BN;
-  const uint32_t t_lane = static_cast<uint32_t>(warp * 32) << 16;   // this warp's quarter of the 128 lanes
-
-  const int req = s_req, mt = tile - a.prefix[req];
-  const int tok0 = a.cu_q[req], qlen = a.cu_q[req + 1] - tok0, L = a.seq_lens[req];
-  const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
-  const int t_first = mt * a.TQ, t_last = min(qlen, t_first + a.TQ) - 1;
-  const int kmax = L - qlen + 1 + t_last;              // keys [0, kmax) are visible to the tile's last token
-  const int nkt = kmax > 0 ? (kmax + PF_BN - 1) / PF_BN : 0;
-
-  // ---- this thread's row ----
-  const int tl = tid / a.G, hg = tid - tl * a.G, tq = t_first + tl;
-  const bool valid = tl < a.TQ && tq < qlen;
-  const int lim = valid ? L - qlen + 1 + tq : 0x7fffffff;   // padding rows hold q = 0 and are never stored
-  float c_row = 0.f;
-  {
-    const __nv_bfloat16* qrow = a.q + static_cast<int64_t>(tok0 + tq) * a.q_st + static_cast<int64_t>(kvh * a.G + hg) * a.q_sh;
-    const float* ksr = a.ks + kvh * (a.pc_k ? D : 1);
-    float amax = 0.f;
-    if (valid) {
-#pragma unroll 4
-      for (int c = 0; c < D / 8; ++c) {
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-        float s[8];
-        if (a.pc_k) {
-          const float4 s0 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c), s1 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c + 1);
-          s[0] = s0.x, s[1] = s0.y, s[2] = s0.z, s[3] = s0.w, s[4] = s1.x, s[5] = s1.y, s[6] = s1.z, s[7] = s1.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) s[e] = 1.f;
-        }
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          amax = fmaxf(amax, fmaxf(fabsf(bf16lo(ww[e]) * s[2 * e]), fabsf(bf16hi(ww[e]) * s[2 * e + 1])));
-      }
-    }
-    // power-of-two row scale that puts the largest |q * s_k| into [2^14, 2^15): fp16 keeps 11 significant bits
-    int ex = 0;
-    if (amax > 0.f) frexpf(amax, &ex);
-    const int sh = amax > 0.f ? max(-60, min(60, 15 - ex)) : 0;
-    const float up = ldexpf(1.f, sh);
-    c_row = a.scale_log2 * ldexpf(1.f, -sh) * (a.pc_k ? 1.f : __ldg(ksr));
-#pragma unroll 2
-    for (int c = 0; c < D / 8; ++c) {
-      uint4 o = make_uint4(0u, 0u, 0u, 0u);
-      if (valid) {
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-        float s[8];
-        if (a.pc_k) {
-          const float4 s0 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c), s1 = __ldg(reinterpret_cast<const float4*>(ksr) + 2 * c + 1);
-          s[0] = s0.x, s[1] = s0.y, s[2] = s0.z, s[3] = s0.w, s[4] = s1.x, s[5] = s1.y, s[6] = s1.z, s[7] = s1.w;
-        } else {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) s[e] = 1.f;
-        }
-        uint32_t oo[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) oo[e] = pack_f16x2(bf16lo(ww[e]) * s[2 * e] * up, bf16hi(ww[e]) * s[2 * e + 1] * up);
-        o = make_uint4(oo[0], oo[1], oo[2], oo[3]);
-      }
-      *reinterpret_cast<uint4*>(p_q + (c >> 3) * (PF_BM * 128) + slab_off(tid, c & 7)) = o;
-    }
-  }
-
-  // ---- TMA producer state (warp 0; lane i < 4 owns the i-th 16-key box of a step) ----
-  auto page_of = [&](int j) {   // page id and offset of this lane's box of step j; boxes past the end re-read the first
-    const int n0 = j * PF_BN, n = n0 + 16 * lane;
-    return (n < L ? n : n0);
-  };
-  int pg_n = 0, pg_nn = 0;      // page ids of steps j + 1 and j + 2
-  auto issue = [&](bool is_k, int j, int page) {
-    const uint32_t bar = is_k ? bar_k : bar_v;
-    if (lane == 0) mbar_expect_tx(bar, Gm::STG_BYTES);
-    __syncwarp();
-    if (lane < 4) {
-      const int off = page_of(j) & a.bs_mask;
-      const int* pos = is_k ? a.kpos : a.vpos;
-      auto coord = [&](int s) { return pos[0] == s ? off : (pos[1] == s ? kvh : page); };
-      tma_load_4d((is_k ? u_sk : u_sv) + lane * 16 * D, is_k ? &tm_k : &tm_v, 0, coord(1), coord(2), coord(3), bar);
-    }
-  };
-  bool ok = true;
-  int k_issued = 0, v_issued = 0, k_waited = 0, v_waited = 0, s_issued = 0, s_waited = 0, o_issued = 0, o_waited = 0;
-  if (warp == 0 && nkt > 0) {
-    int pg0 = 0;
-    if (lane < 4) {
-      pg0 = bt[page_of(0) >> a.lbs];
-      if (nkt > 1) pg_n = bt[page_of(1) >> a.lbs];
-    }
-    issue(true, 0, pg0);
-    issue(false, 0, pg0);
-  }
-  if (nkt > 0) k_issued = v_issued = 1;
-
-  float m_ref = -1e30f, l_sum = 0.f;   // running maximum (log2 domain, held back) and denominator
-  constexpr uint32_t ID_S = instr_desc(PF_BM, PF_BN, false), ID_O = instr_desc(PF_BM, D, true);
-
-  for (int j = 0; j < nkt; ++j) {
-    const uint32_t par = j & 1;
-    if (warp == 0 && lane < 4 && j + 2 < nkt) pg_nn = bt[page_of(j + 2) >> a.lbs];
-    // -- K of this step: widen, then S = Q.K^T on the tensor core --
-    ok = ok && mbar_wait(bar_k, par);
-    ++k_waited;
-    if (ok) widen_tile<D>(p_sk, p_k, tid);
-    fence_proxy_async();   // generic-proxy writes of the operand tiles (and of q before the first step) -> tensor core
-    tc_fence_before();
-    ok = __syncthreads_and(ok);
-    if (!ok) break;
-    if (warp == 0) {
-      if (j + 1 < nkt) issue(true, j + 1, pg_n);
-      if (lane == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16(t_s, smem_desc(u_q + sl * (PF_BM * 128) + ks * 32, 16, 1024),
-                     smem_desc(u_k + sl * Gm::KV_SLAB + ks * 32, 16, 1024), ID_S, (sl | ks) ? 1u : 0u);
-        umma_commit(bar_s);
-      }
-    }
-    if (j + 1 < nkt) ++k_issued;
-    ++s_issued;
-    // -- V of this step (the previous step's P.V must have finished reading the V and P tiles) --
-    if (j > 0) {
-      ok = ok && mbar_wait(bar_o, (j - 1) & 1);
-      ++o_waited;
-    }
-    ok = ok && mbar_wait(bar_v, par);
-    ++v_waited;
-    if (ok) widen_tile<D>(p_sv, p_v, tid);
-    // -- softmax of this thread's row --
-    ok = ok && mbar_wait(bar_s, par);
-    ++s_waited;
-    tc_fence_after();
-    if (__syncthreads_and(ok) == 0) {
-      ok = false;
-      break;
-    }
-    uint32_t sr[PF_BN];
-    {
-      uint32_t lo[32], hi[32];
-      tmem_ld32(t_s + t_lane, lo);
-      tmem_ld32(t_s + t_lane + 32, hi);
-      tmem_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 32; ++i) sr[i] = lo[i], sr[32 + i] = hi[i];
-    }
-    const int n_base = j * PF_BN;
-    float mx = -INFINITY;
-    if (n_base + PF_BN <= lim) {
-#pragma unroll
-      for (int i = 0; i < PF_BN; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
-    } else {
-#pragma unroll
-      for (int i = 0; i < PF_BN; ++i) {
-        if (n_base + i >= lim) sr[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
-        mx = fmaxf(mx, __uint_as_float(sr[i]));
-      }
-    }
-    // scores are S * c_row with c_row > 0, so the row maximum of S gives the maximum score
-    const float tile_max = mx * c_row;
-    const bool grow = tile_max > m_ref + 8.f;
-    float alpha = 1.f;
-    if (grow) {
-      alpha = ex2(m_ref - tile_max);   // 0 on the first step (m_ref = -1e30)
-      m_ref = tile_max;
-      l_sum *= alpha;
-    }
-    if (j > 0 && __any_sync(0xffffffffu, grow)) {   // rescale the accumulator rows of this warp in tensor memory
-#pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
-        uint32_t o[32];
-        tmem_ld32(t_o + t_lane + c, o);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-        tmem_st32(t_o + t_lane + c, o);
-      }
-      tmem_wait_st();
-    }
-    {
-      const float nm = -m_ref;
-      float ls = 0.f;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e]), c_row, nm));
-          const float p1 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e + 1]), c_row, nm));
-          ls += p0 + p1;
-          w[e] = pack_f16x2(p0, p1);
-        }
-        *reinterpret_cast<uint4*>(p_p + slab_off(tid, c)) = make_uint4(w[0], w[1], w[2], w[3]);
-      }
-      l_sum += ls;
-    }
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) {
-      if (j + 1 < nkt) issue(false, j + 1, pg_n);
-      if (lane == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16(t_o, smem_desc(u_p + ks * 32, 16, 1024), smem_desc(u_v + ks * 16 * 128, Gm::KV_SLAB, 1024), ID_O,
-                   (j | ks) ? 1u : 0u);
-        umma_commit(bar_o);
-      }
-      pg_n = pg_nn;
-    }
-    if (j + 1 < nkt) ++v_issued;
-    ++o_issued;
-  }
-
-  // ---- epilogue: O / denominator * s_v -> bf16 ----
-  if (ok && nkt > 0) {
-    ok = mbar_wait(bar_o, (nkt - 1) & 1);
-    ++o_waited;
-    tc_fence_after();
-  }
-  ok = __syncthreads_and(ok);
-  if (ok) {
-    __nv_bfloat16* orow = a.out + static_cast<int64_t>(tok0 + tq) * a.o_st + static_cast<int64_t>(kvh * a.G + hg) * a.o_sh;
-    const float inv = 1.f / fmaxf(l_sum, 1e-30f);
-    const float* vsr = a.vs + kvh * (a.pc_v ? D : 1);
-#pragma unroll 1
-    for (int c = 0; c < D; c += 32) {
-      uint32_t o[32];
-      if (nkt > 0) {
-        tmem_ld32(t_o + t_lane + c, o);
-        tmem_wait_ld();
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] = 0u;
-      }
-      if (valid) {
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          float sv[8];
-          if (a.pc_v) {
-            const float4 s0 = __ldg(reinterpret_cast<const float4*>(vsr + c + i)), s1 = __ldg(reinterpret_cast<const float4*>(vsr + c + i + 4));
-            sv[0] = s0.x, sv[1] = s0.y, sv[2] = s0.z, sv[3] = s0.w, sv[4] = s1.x, sv[5] = s1.y, sv[6] = s1.z, sv[7] = s1.w;
-          } else {
-            const float one = __ldg(vsr);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) sv[e] = one;
-          }
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e)
-            w[e] = pack_bf16x2(__uint_as_float(o[i + 2 * e]) * inv * sv[2 * e], __uint_as_float(o[i + 2 * e + 1]) * inv * sv[2 * e + 1]);
-          *reinterpret_cast<uint4*>(orow + c + i) = make_uint4(w[0], w[1], w[2], w[3]);
-        }
-      }
-    }
-  } else {
-    // A bounded wait expired: report it, then give every copy and tensor-core operation that is still in flight
-    // one more bounded chance to finish before shared and tensor memory are released.
-    if (tid == 0) atomicExch(a.hdr, 1);
-    if (k_issued > k_waited) mbar_wait(bar_k, k_waited & 1);
-    if (v_issued > v_waited) mbar_wait(bar_v, v_waited & 1);
-    if (s_issued > s_waited) mbar_wait(bar_s, s_waited & 1);
-    if (o_issued > o_waited) mbar_wait(bar_o, o_waited & 1);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, PF_TMEM_COLS);
-}
-
-// ------------------------------------------------------------------------------------------------------
-// warp-specialized variant: two m tiles per CTA share one K/V stream
+// warp-specialized kernel: two m tiles per CTA share one K/V stream
 // ------------------------------------------------------------------------------------------------------
 // 13 warps: warps 0-3 and 4-7 are the softmax groups of m tile 0 and 1 (one thread per row), warps 8-11 widen the
 // int8 K/V boxes into fp16 operand tiles and issue the TMA loads, warp 12 (one lane) issues every tcgen05.mma.
-// The groups meet only through mbarriers, so S = Q.K^T of step j + 1 runs on the tensor core while the softmax
-// groups work on step j, and O += P.V of step j starts the moment a group has written its P.
-//   TMEM: S[tile][step & 1] 4 x 64 columns, O[tile] 2 x D columns.
-//   smem: Q 2 tiles, fp16 K and V 2 stages each, P 2 buffers per tile, int8 landing zones 2 stages each.
+// The groups meet only through mbarriers. Steps are 128 keys. Per m tile the chain is S = Q.K^T -> softmax ->
+// O += P.V; the tensor core works on one tile's products while the other tile is in its softmax (the two chains run
+// half a step apart), and the converters run up to two steps ahead.
+//   TMEM (512 columns): S[tile] 2 x 128 fp32 columns, O[tile] 2 x D. P (fp16 pairs, 64 columns) is written over the
+//     first half of its tile's S and is the A operand of P.V straight from tensor memory.
+//   smem: Q 2 tiles, fp16 K and V 2 stages each, one int8 landing zone each for K and V.
+// A tcgen05.mma of 128 x N x 16 with N <= 128 occupies the tensor core for ~90 cycles however small N is (measured),
+// so steps of 128 keys (N = 128 for S) halve the cost of S against 64-key steps.
+constexpr int WS_BN = 128;           // keys per step
 constexpr int WS_THREADS = 13 * 32;
+constexpr int WS_TMEM_COLS = 512;
 #ifdef KVQ_PF_TIMELINE
 __device__ long long g_pf_timeline[3 * 64 * 8];   // [role][step][event]
 #define PF_TL(role, step, ev)                                                                      \
@@ -535,43 +187,37 @@ __device__ long long g_pf_timeline[3 * 64 * 8];   // [role][step][event]
 #else
 #define PF_TL(role, step, ev) do { } while (0)
 #endif
-constexpr int WS_TMEM_COLS = 512;
 enum WsBar {
-  WB_STGK = 0,       // [2] int8 K boxes landed (TMA)
-  WB_STGV = 2,       // [2]
-  WB_KF_READY = 4,   // [2] fp16 K tile written (128 converter threads)
-  WB_VF_READY = 6,   // [2]
-  WB_KF_FREE = 8,    // [2] tensor core done with the fp16 K tile (commit)
-  WB_VF_FREE = 10,   // [2]
-  WB_S_READY = 12,   // [tile * 2 + buffer] S computed (commit)
-  WB_S_FREE = 16,    // [tile * 2 + buffer] S read into registers (128 softmax threads)
-  WB_P_READY = 20,   // [tile * 2 + buffer] P written (128 softmax threads)
-  WB_O_DONE = 24,    // [tile * 2 + (step & 1)] O += P.V of that step finished (commit)
-  WB_Q_READY = 28,   // q tiles written (256 softmax threads)
-  WB_STGK_FREE = 29, // [2] landing zone read by every converter (128 threads)
-  WB_STGV_FREE = 31, // [2]
-  WB_COUNT = 33
+  WB_STGK = 0,        // int8 K boxes of a step landed (TMA)
+  WB_STGV = 1,
+  WB_STGK_FREE = 2,   // landing zone read by every converter (128 threads)
+  WB_STGV_FREE = 3,
+  WB_KF_READY = 4,    // [2] fp16 K tile written (128 converter threads)
+  WB_VF_READY = 6,    // [2]
+  WB_KF_FREE = 8,     // [2] tensor core done with the fp16 K tile (commit)
+  WB_VF_FREE = 10,    // [2]
+  WB_S_READY = 12,    // [tile] S of the step computed (commit)
+  WB_P_READY = 14,    // [tile * 2 + half] P of 64 keys of the step written to tensor memory (128 softmax threads)
+  WB_O_DONE = 18,     // [tile] O += P.V of the step finished (commit)
+  WB_Q_READY = 20,    // q tiles written (256 softmax threads)
+  WB_COUNT = 21
 };
 
 template <int D>
 struct WsGeom {
   static constexpr int NSLAB = D / 64;
   static constexpr int Q_TILE = NSLAB * PF_BM * 128;
-  static constexpr int KV_SLAB = PF_BN * 128;
+  static constexpr int KV_SLAB = WS_BN * 128;      // [128 keys][64 channels] fp16
   static constexpr int KV_TILE = NSLAB * KV_SLAB;
-  static constexpr int P_TILE = PF_BM * 128;
-  static constexpr int STG = PF_BN * D;
-  static constexpr int OFF_Q = 0, OFF_K = OFF_Q + 2 * Q_TILE, OFF_V = OFF_K + 2 * KV_TILE, OFF_P = OFF_V + 2 * KV_TILE,
-                       OFF_SK = OFF_P + 4 * P_TILE, OFF_SV = OFF_SK + 2 * STG, END = OFF_SV + 2 * STG;
+  static constexpr int STG = WS_BN * D;            // int8 landing zone of one K or V step (eight 16-key boxes)
+  static constexpr int OFF_Q = 0, OFF_K = OFF_Q + 2 * Q_TILE, OFF_V = OFF_K + 2 * KV_TILE, OFF_SK = OFF_V + 2 * KV_TILE,
+                       OFF_SV = OFF_SK + STG, END = OFF_SV + STG;
   static constexpr int SMEM = 1024 + END;
 };
 
-// Bounded wait that also gives up as soon as any thread of the CTA has given up. Called by converged warps; the
-// result is uniform over the warp, so the warp-collective tensor-memory instructions that follow stay converged.
-__device__ __forceinline__ bool ws_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag);
-__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  return __all_sync(0xffffffffu, ws_wait_thread(bar, parity, abort_flag));
-}
+// Bounded wait that also gives up as soon as any thread of the CTA has given up. ws_wait is called by converged
+// warps and returns a warp-uniform result, so the warp-collective tensor-memory instructions that follow stay
+// converged.
 __device__ __forceinline__ bool ws_wait_thread(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
@@ -585,6 +231,45 @@ __device__ __forceinline__ bool ws_wait_thread(uint32_t bar, uint32_t parity, vo
       return false;
     }
   }
+}
+__device__ __forceinline__ bool ws_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, ws_wait_thread(bar, parity, abort_flag));
+}
+
+// int8 landing zone (TMA boxes of [16 keys][D bytes], hardware-swizzled) of WS_BN keys -> fp16 operand slabs.
+// 16 channels per item; called by the 128 converter threads.
+template <int D>
+__device__ __forceinline__ void widen_step(const uint8_t* stg, uint8_t* dst, int tid) {
+  constexpr int CPR = D / 16;
+#pragma unroll
+  for (int i = 0; i < WS_BN * CPR / 128; ++i) {
+    const int idx = tid + 128 * i, key = idx / CPR, c = idx - key * CPR, kk = key & 15;
+    const uint32_t src = (key >> 4) * 16 * D + kk * D + ((D == 128 ? (c ^ (kk & 7)) : (c ^ ((kk >> 1) & 3))) << 4);
+    const uint4 w = *reinterpret_cast<const uint4*>(stg + src);
+    uint4 lo, hi;
+    i8x4_to_f16x4(w.x, lo.x, lo.y);
+    i8x4_to_f16x4(w.y, lo.z, lo.w);
+    i8x4_to_f16x4(w.z, hi.x, hi.y);
+    i8x4_to_f16x4(w.w, hi.z, hi.w);
+    uint8_t* slab = dst + (c >> 2) * WsGeom<D>::KV_SLAB;
+    *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2)) = lo;
+    *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2 + 1)) = hi;
+  }
+}
+
+// D[tmem] (+)= A[tmem] . B[smem]: A is 128 lanes x 8 columns of packed fp16 pairs (k = 2 * column, 2 * column + 1).
+__device__ __forceinline__ void umma_f16_ts(uint32_t d, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t addr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(addr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]),
+      "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
 }
 
 template <int D>
@@ -613,10 +298,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
   if (tid == 0) {
     s_abort = 0;
     for (int i = 0; i < WB_COUNT; ++i) {
-      const int n = (i >= WB_KF_READY && i < WB_KF_FREE) || (i >= WB_S_FREE && i < WB_O_DONE) || i >= WB_STGK_FREE
-                        ? 128
-                        : (i == WB_Q_READY ? 256 : 1);
-      mbar_init(bar(i), n);
+      const bool by_group = i == WB_STGK_FREE || i == WB_STGV_FREE || (i >= WB_KF_READY && i < WB_KF_FREE) ||
+                            (i >= WB_P_READY && i < WB_O_DONE);   // arrivals from a 128-thread group
+      mbar_init(bar(i), by_group ? 128 : (i == WB_Q_READY ? 256 : 1));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -637,18 +321,17 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     const int t_first = mt * a.TQ;
     if (t_first >= qlen) return 0;
     const int kmax = L - qlen + 1 + min(qlen, t_first + a.TQ) - 1;
-    return kmax > 0 ? (kmax + PF_BN - 1) / PF_BN : 0;
+    return kmax > 0 ? (kmax + WS_BN - 1) / WS_BN : 0;
   };
   const int nk0 = steps_of(mt0), nk1 = steps_of(mt0 + 1), nk = max(nk0, nk1);
-  constexpr uint32_t ID_S = instr_desc(PF_BM, PF_BN, false), ID_O = instr_desc(PF_BM, D, true);
+  constexpr uint32_t ID_S = instr_desc(PF_BM, WS_BN, false), ID_O = instr_desc(PF_BM, D, true);
 
   if (warp < 8) {
     // ================= softmax group of m tile t =================
     const int t = warp >> 2, row = tid & 127, mt = mt0 + t, nkt = t ? nk1 : nk0;
     uint8_t* p_q = p_base + Gm::OFF_Q + t * Gm::Q_TILE;
-    uint8_t* p_p = p_base + Gm::OFF_P + t * 2 * Gm::P_TILE;   // two buffers, by step parity
     const uint32_t t_lane = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t t_s = tmem + t * 2 * PF_BN + t_lane, t_o = tmem + 4 * PF_BN + t * D + t_lane;
+    const uint32_t t_s = tmem + t * WS_BN + t_lane, t_o = tmem + 2 * WS_BN + t * D + t_lane;
     const int tl = row / a.G, hg = row - tl * a.G, tq = mt * a.TQ + tl;
     const bool valid = tl < a.TQ && tq < qlen;
     const int lim = valid ? L - qlen + 1 + tq : 0x7fffffff;   // padding rows hold q = 0 and are never stored
@@ -700,37 +383,40 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     float m_ref = -1e30f, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < nkt && ok; ++j) {
-      const int b = j & 1;
       if (tid == 0) PF_TL(0, j, 0);
-      ok = ws_wait(bar(WB_S_READY + t * 2 + b), (j >> 1) & 1, abort_flag);
+      ok = ws_wait(bar(WB_S_READY + t), j & 1, abort_flag);
       if (!ok) break;
       if (tid == 0) PF_TL(0, j, 1);
       tc_fence_after();
-      uint32_t sr[PF_BN];
-      {
-        uint32_t lo[32], hi[32];
-        tmem_ld32(t_s + b * PF_BN, lo);
-        tmem_ld32(t_s + b * PF_BN + 32, hi);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sr[i] = lo[i], sr[32 + i] = hi[i];
-      }
-      tc_fence_before();
-      if (tid == 0) PF_TL(0, j, 2);
-      mbar_arrive(bar(WB_S_FREE + t * 2 + b));
-      if (tid == 0) PF_TL(0, j, 3);
-      const int n_base = j * PF_BN;
+      // pass 1: row maximum of the step's 128 scores (64 columns per round trip to tensor memory)
+      const int n_base = j * WS_BN;
+      const bool masked = n_base + WS_BN > lim;
       float mx = -INFINITY;
-      if (n_base + PF_BN <= lim) {
+      {
+        float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-        for (int i = 0; i < PF_BN; ++i) mx = fmaxf(mx, __uint_as_float(sr[i]));
-      } else {
+        for (int c = 0; c < WS_BN; c += 64) {
+          uint32_t sa[32], sb[32];
+          tmem_ld32(t_s + c, sa);
+          tmem_ld32(t_s + c + 32, sb);
+          tmem_wait_ld();
+          if (!masked) {
 #pragma unroll
-        for (int i = 0; i < PF_BN; ++i) {
-          if (n_base + i >= lim) sr[i] = 0xff800000u;   // -inf: exp2 gives exactly 0
-          mx = fmaxf(mx, __uint_as_float(sr[i]));
+            for (int i = 0; i < 32; i += 2) {
+              m4[(i >> 1) & 3] = fmaxf(m4[(i >> 1) & 3], fmaxf(__uint_as_float(sa[i]), __uint_as_float(sa[i + 1])));
+              m4[(i >> 1) & 3] = fmaxf(m4[(i >> 1) & 3], fmaxf(__uint_as_float(sb[i]), __uint_as_float(sb[i + 1])));
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (n_base + c + i < lim) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sa[i]));
+              if (n_base + c + 32 + i < lim) m4[i & 3] = fmaxf(m4[i & 3], __uint_as_float(sb[i]));
+            }
+          }
         }
+        mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
+      if (tid == 0) PF_TL(0, j, 2);
       const float tile_max = mx * c_row;   // c_row > 0
       const bool grow = tile_max > m_ref + 8.f;
       float alpha = 1.f;
@@ -739,54 +425,55 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         m_ref = tile_max;
         l_sum *= alpha;
       }
-      if (tid == 0) PF_TL(0, j, 4);
-      if (j >= 2) {   // P.V of step j - 2 has finished reading this step's P buffer
-        ok = ws_wait(bar(WB_O_DONE + t * 2 + b), ((j - 2) >> 1) & 1, abort_flag);
-        if (!ok) break;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {   // rescale O (rare after the first steps): P.V of step j - 1 first
-        ok = ws_wait(bar(WB_O_DONE + t * 2 + (b ^ 1)), ((j - 1) >> 1) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        {
+      // S of this step is committed after O += P.V of the previous step, so O may be rescaled here
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            uint32_t o[32];
-            tmem_ld32(t_o + c, o);
-            tmem_wait_ld();
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld32(t_o + c, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(t_o + c, o);
-          }
-          tmem_wait_st();
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(t_o + c, o);
         }
       }
-      if (tid == 0) PF_TL(0, j, 5);
+      if (tid == 0) PF_TL(0, j, 3);
+      // pass 2: P = exp2(S * c_row - m_ref) as fp16 pairs, written over the first half of S chunk by chunk
+      // (chunk i reads S columns [32 i, 32 i + 32) and then writes P columns [16 i, 16 i + 16): never ahead of a
+      // read). P.V may start on the first 64 keys while the last 64 are still being computed.
       {
         const float nm = -m_ref;
         float ls = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < WS_BN; c += 32) {
+          uint32_t sr[32];
+          tmem_ld32(t_s + c, sr);
+          tmem_wait_ld();
+          uint32_t w[16];
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float p0 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e]), c_row, nm));
-            const float p1 = ex2(fmaf(__uint_as_float(sr[8 * c + 2 * e + 1]), c_row, nm));
+          for (int i = 0; i < 16; ++i) {
+            float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), c_row, nm));
+            float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), c_row, nm));
+            if (masked) {
+              p0 = n_base + c + 2 * i < lim ? p0 : 0.f;
+              p1 = n_base + c + 2 * i + 1 < lim ? p1 : 0.f;
+            }
             ls += p0 + p1;
-            w[e] = pack_f16x2(p0, p1);
+            w[i] = pack_f16x2(p0, p1);
           }
-          *reinterpret_cast<uint4*>(p_p + b * Gm::P_TILE + slab_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+          tmem_st16(t_s + (c >> 1), w);
+          if (c & 32) {   // 64 keys of P complete
+            tmem_wait_st();
+            tc_fence_before();
+            mbar_arrive(bar(WB_P_READY + t * 2 + (c >> 6)));
+          }
         }
         l_sum += ls;
       }
-      if (tid == 0) PF_TL(0, j, 6);
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(bar(WB_P_READY + t * 2 + b));
-      if (tid == 0) PF_TL(0, j, 7);
+      if (tid == 0) PF_TL(0, j, 4);
     }
     // ---- epilogue: O / denominator * s_v -> bf16 ----
-    if (ok && nkt > 0) ok = ws_wait(bar(WB_O_DONE + t * 2 + ((nkt - 1) & 1)), ((nkt - 1) >> 1) & 1, abort_flag);
+    if (ok && nkt > 0) ok = ws_wait(bar(WB_O_DONE + t), (nkt - 1) & 1, abort_flag);
     if (ok && nkt > 0) {
       tc_fence_after();
       __nv_bfloat16* orow = a.out + static_cast<int64_t>(tok0 + tq) * a.o_st + static_cast<int64_t>(kvh * a.G + hg) * a.o_sh;
@@ -826,73 +513,68 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     const int ctid = tid - 256;
     const bool issuer = warp == 8;
     auto key_of = [&](int j) {   // first key of this lane's 16-key box of step j; boxes past the end re-read the first
-      const int n0 = j * PF_BN, n = n0 + 16 * lane;
+      const int n0 = j * WS_BN, n = n0 + 16 * lane;
       return n < L ? n : n0;
     };
-    auto issue = [&](bool is_k, int j, int page) {   // warp 8: lane i < 4 loads the i-th box
-      const uint32_t full = bar((is_k ? WB_STGK : WB_STGV) + (j & 1));
+    auto issue = [&](bool is_k, int j, int page) {   // warp 8: lane i < 8 loads the i-th box
+      const uint32_t full = bar(is_k ? WB_STGK : WB_STGV);
       if (lane == 0) mbar_expect_tx(full, Gm::STG);
       __syncwarp();
-      if (lane < 4) {
+      if (lane < 8) {
         const int off = key_of(j) & a.bs_mask;
         const int* pos = is_k ? a.kpos : a.vpos;
         auto coord = [&](int s) { return pos[0] == s ? off : (pos[1] == s ? kvh : page); };
-        tma_load_4d(base + (is_k ? Gm::OFF_SK : Gm::OFF_SV) + (j & 1) * Gm::STG + lane * 16 * D, is_k ? &tm_k : &tm_v, 0,
-                    coord(1), coord(2), coord(3), full);
+        tma_load_4d(base + (is_k ? Gm::OFF_SK : Gm::OFF_SV) + lane * 16 * D, is_k ? &tm_k : &tm_v, 0, coord(1), coord(2),
+                    coord(3), full);
       }
     };
-    int pg_a = 0, pg_b = 0;   // page ids (lanes 0-3 of warp 8) of the next two steps to issue
+    int pg_a = 0, pg_b = 0;   // page ids (lanes 0-7 of warp 8) of the next two steps to issue
     if (issuer) {
-      if (lane < 4) {
-        if (nk > 0) pg_a = bt[key_of(0) >> a.lbs];
-        if (nk > 1) pg_b = bt[key_of(1) >> a.lbs];
-      }
+      if (lane < 8 && nk > 0) pg_a = bt[key_of(0) >> a.lbs];
       if (nk > 0) issue(true, 0, pg_a), issue(false, 0, pg_a);
-      if (nk > 1) issue(true, 1, pg_b), issue(false, 1, pg_b);
-      pg_a = 0, pg_b = 0;
-      if (lane < 4) {
-        if (nk > 2) pg_a = bt[key_of(2) >> a.lbs];
-        if (nk > 3) pg_b = bt[key_of(3) >> a.lbs];
+      pg_a = pg_b = 0;
+      if (lane < 8) {
+        if (nk > 1) pg_a = bt[key_of(1) >> a.lbs];
+        if (nk > 2) pg_b = bt[key_of(2) >> a.lbs];
       }
     }
     bool ok = true;
     for (int j = 0; j < nk && ok; ++j) {
       const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      // pg_a belongs to step j + 2 (issued below), pg_b to step j + 3
+      // pg_a belongs to step j + 1 (issued below), pg_b to step j + 2
       if (ctid == 0) PF_TL(1, j, 0);
-      ok = ws_wait(bar(WB_STGK + s), ph, abort_flag);
+      ok = ws_wait(bar(WB_STGK), j & 1, abort_flag);
       if (ctid == 0) PF_TL(1, j, 1);
       if (ok && j >= 2) ok = ws_wait(bar(WB_KF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
       if (ctid == 0) PF_TL(1, j, 2);
-      widen_tile<D>(p_base + Gm::OFF_SK + s * Gm::STG, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
+      widen_step<D>(p_base + Gm::OFF_SK, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
       fence_proxy_async();
       mbar_arrive(bar(WB_KF_READY + s));
-      mbar_arrive(bar(WB_STGK_FREE + s));
+      mbar_arrive(bar(WB_STGK_FREE));
       if (ctid == 0) PF_TL(1, j, 3);
-      if (issuer && j + 2 < nk) {   // every converter has left the landing zone before it is refilled
-        ok = ws_wait(bar(WB_STGK_FREE + s), ph, abort_flag);
-        if (ok) issue(true, j + 2, pg_a);
+      if (issuer && j + 1 < nk) {   // every converter has left the landing zone before it is refilled
+        ok = ws_wait(bar(WB_STGK_FREE), j & 1, abort_flag);
+        if (ok) issue(true, j + 1, pg_a);
       }
       if (ctid == 0) PF_TL(1, j, 4);
-      ok = ws_wait(bar(WB_STGV + s), ph, abort_flag);
+      ok = ok && ws_wait(bar(WB_STGV), j & 1, abort_flag);
       if (ctid == 0) PF_TL(1, j, 5);
       if (ok && j >= 2) ok = ws_wait(bar(WB_VF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
       if (ctid == 0) PF_TL(1, j, 6);
-      widen_tile<D>(p_base + Gm::OFF_SV + s * Gm::STG, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
+      widen_step<D>(p_base + Gm::OFF_SV, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
       fence_proxy_async();
       mbar_arrive(bar(WB_VF_READY + s));
-      mbar_arrive(bar(WB_STGV_FREE + s));
+      mbar_arrive(bar(WB_STGV_FREE));
       if (ctid == 0) PF_TL(1, j, 7);
       if (issuer) {
-        if (j + 2 < nk) {
-          ok = ok && ws_wait(bar(WB_STGV_FREE + s), ph, abort_flag);
-          if (ok) issue(false, j + 2, pg_a);
+        if (j + 1 < nk) {
+          ok = ws_wait(bar(WB_STGV_FREE), j & 1, abort_flag);
+          if (ok) issue(false, j + 1, pg_a);
         }
         pg_a = pg_b;
-        pg_b = (lane < 4 && j + 4 < nk) ? bt[key_of(j + 4) >> a.lbs] : 0;
+        pg_b = (lane < 8 && j + 3 < nk) ? bt[key_of(j + 3) >> a.lbs] : 0;
       }
     }
   } else if (lane == 0) {
@@ -901,52 +583,55 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     // Descriptors differ only in their 14-bit start-address field (address >> 4): one base per operand, the
     // tile / slab / k-step offsets (compile-time constants once the loops are unrolled) are added to it.
     const uint64_t d_q = smem_desc(base + Gm::OFF_Q, 16, 1024), d_k = smem_desc(base + Gm::OFF_K, 16, 1024),
-                   d_p = smem_desc(base + Gm::OFF_P, 16, 1024), d_v = smem_desc(base + Gm::OFF_V, Gm::KV_SLAB, 1024);
-    auto issue_qk = [&](int j) {
+                   d_v = smem_desc(base + Gm::OFF_V, Gm::KV_SLAB, 1024);
+    auto issue_qk = [&](int t, int j) {   // S[t] = Q[t] . K(j)^T
       const int s = j & 1;
       ok = ok && ws_wait_thread(bar(WB_KF_READY + s), (j >> 1) & 1, abort_flag);
+      if (!ok) return;
+      tc_fence_after();
       const uint64_t d_ks = d_k + static_cast<uint64_t>((s * Gm::KV_TILE) >> 4);
+      const uint64_t d_qt = d_q + static_cast<uint64_t>((t * Gm::Q_TILE) >> 4);
 #pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        if (!ok || j >= (t ? nk1 : nk0)) continue;
-        if (j >= 2) ok = ws_wait_thread(bar(WB_S_FREE + t * 2 + s), ((j - 2) >> 1) & 1, abort_flag);
-        if (!ok) continue;
-        tc_fence_after();
-        const uint32_t d_s = tmem + (t * 2 + s) * PF_BN;
+      for (int sl = 0; sl < NSLAB; ++sl)
 #pragma unroll
-        for (int sl = 0; sl < NSLAB; ++sl)
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            umma_f16(d_s, d_q + static_cast<uint64_t>((t * Gm::Q_TILE + sl * (PF_BM * 128) + ks * 32) >> 4),
-                     d_ks + static_cast<uint64_t>((sl * Gm::KV_SLAB + ks * 32) >> 4), ID_S, (sl | ks) ? 1u : 0u);
-        umma_commit(bar(WB_S_READY + t * 2 + s));
-      }
-      if (ok) umma_commit(bar(WB_KF_FREE + s));
+        for (int ks = 0; ks < 4; ++ks)
+          umma_f16(tmem + t * WS_BN, d_qt + static_cast<uint64_t>((sl * (PF_BM * 128) + ks * 32) >> 4),
+                   d_ks + static_cast<uint64_t>((sl * Gm::KV_SLAB + ks * 32) >> 4), ID_S, (sl | ks) ? 1u : 0u);
+      umma_commit(bar(WB_S_READY + t));
     };
-    if (ok && nk > 0) issue_qk(0);
+    if (ok && nk0 > 0) issue_qk(0, 0);
+    if (ok && nk1 > 0) issue_qk(1, 0);
+    if (ok && nk > 0) umma_commit(bar(WB_KF_FREE));
     for (int j = 0; j < nk && ok; ++j) {
       const int s = j & 1;
       PF_TL(2, j, 0);
-      if (j + 1 < nk) issue_qk(j + 1);
+      ok = ws_wait_thread(bar(WB_VF_READY + s), (j >> 1) & 1, abort_flag);
       PF_TL(2, j, 1);
-      ok = ok && ws_wait_thread(bar(WB_VF_READY + s), (j >> 1) & 1, abort_flag);
-      PF_TL(2, j, 2);
       const uint64_t d_vs = d_v + static_cast<uint64_t>((s * Gm::KV_TILE) >> 4);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
-        if (!ok || j >= (t ? nk1 : nk0)) continue;
-        ok = ws_wait_thread(bar(WB_P_READY + t * 2 + s), (j >> 1) & 1, abort_flag);
-        if (!ok) continue;
-        tc_fence_after();
-        const uint64_t d_ps = d_p + static_cast<uint64_t>(((t * 2 + s) * Gm::P_TILE) >> 4);
+        const int nkt = t ? nk1 : nk0;
+        if (!ok || j >= nkt) continue;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16(tmem + 4 * PF_BN + t * D, d_ps + static_cast<uint64_t>((ks * 32) >> 4),
-                   d_vs + static_cast<uint64_t>((ks * 16 * 128) >> 4), ID_O, (j | ks) ? 1u : 0u);
-        umma_commit(bar(WB_O_DONE + t * 2 + s));
-        PF_TL(2, j, 3 + t);
+        for (int h = 0; h < 2; ++h) {
+          ok = ok && ws_wait_thread(bar(WB_P_READY + t * 2 + h), j & 1, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          if (h == 0) PF_TL(2, j, 2 + 2 * t);
+#pragma unroll
+          for (int ks = 4 * h; ks < 4 * h + 4; ++ks)   // 16 keys = 8 columns of packed P per k step
+            umma_f16_ts(tmem + 2 * WS_BN + t * D, tmem + t * WS_BN + ks * 8,
+                        d_vs + static_cast<uint64_t>((ks * 16 * 128) >> 4), ID_O, (j | ks) ? 1u : 0u);
+        }
+        if (!ok) continue;
+        umma_commit(bar(WB_O_DONE + t));
+        if (j + 1 < nkt) issue_qk(t, j + 1);   // executes after the P.V above: S[t] (and the P inside it) is free again
+        PF_TL(2, j, 3 + 2 * t);
       }
-      if (ok) umma_commit(bar(WB_VF_FREE + s));
+      if (ok) {
+        umma_commit(bar(WB_VF_FREE + s));
+        if (j + 1 < nk) umma_commit(bar(WB_KF_FREE + (s ^ 1)));
+      }
     }
   }
 
@@ -1025,8 +710,6 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_prefill_attention
   int dev = 0;
   KVQ_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !g_pf_ready[dev]) {
-    KVQ_CUDA(cudaFuncSetAttribute(prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeom<64>::SMEM));
-    KVQ_CUDA(cudaFuncSetAttribute(prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfGeom<128>::SMEM));
     KVQ_CUDA(cudaFuncSetAttribute(prefill_ws_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<64>::SMEM));
     KVQ_CUDA(cudaFuncSetAttribute(prefill_ws_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, WsGeom<128>::SMEM));
     g_pf_ready[dev] = true;
@@ -1052,29 +735,17 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_prefill_attention
                                     vc_stride_h, 1, &tm_v, a.vpos)) != KVQ_OK)
     return rc;
 
-  // KVQ_PREFILL_SIMPLE=1 selects the one-m-tile-per-CTA kernel without warp specialization (debugging aid)
-  static const bool simple = [] {
-    const char* e = getenv("KVQ_PREFILL_SIMPLE");
-    return e && e[0] == '1';
-  }();
-  const int per_cta = simple ? 1 : 2;
+  constexpr int per_cta = 2;   // m tiles per CTA
   prefill_plan_kernel<<<1, 256, 0, s>>>(cu_q, num_seqs, a.TQ, a.min_q, per_cta, a.hdr, a.prefix);
   KVQ_CUDA(cudaGetLastError());
   // upper bound of the work items: sum over requests of ceil(m tiles / per_cta), m tiles = ceil(q_len / TQ)
   const int64_t max_items = total_query_tokens / (static_cast<int64_t>(a.TQ) * per_cta) + num_seqs;
   KVQ_REQUIRE(max_items * num_kv_heads < (1ll << 31), "prefill_attention: batch too large");
   const dim3 grid(static_cast<unsigned>(max_items * num_kv_heads));
-  if (simple) {
-    if (head_dim == 128)
-      KVQ_CUDA(pf_launch_pdl(prefill_kernel<128>, grid, dim3(PF_THREADS), PfGeom<128>::SMEM, s, a, tm_k, tm_v));
-    else
-      KVQ_CUDA(pf_launch_pdl(prefill_kernel<64>, grid, dim3(PF_THREADS), PfGeom<64>::SMEM, s, a, tm_k, tm_v));
-  } else {
-    if (head_dim == 128)
-      KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<128>, grid, dim3(WS_THREADS), WsGeom<128>::SMEM, s, a, tm_k, tm_v));
-    else
-      KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<64>, grid, dim3(WS_THREADS), WsGeom<64>::SMEM, s, a, tm_k, tm_v));
-  }
+  if (head_dim == 128)
+    KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<128>, grid, dim3(WS_THREADS), WsGeom<128>::SMEM, s, a, tm_k, tm_v));
+  else
+    KVQ_CUDA(pf_launch_pdl(prefill_ws_kernel<64>, grid, dim3(WS_THREADS), WsGeom<64>::SMEM, s, a, tm_k, tm_v));
   return KVQ_OK;
 }
 

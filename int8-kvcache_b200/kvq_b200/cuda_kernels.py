@@ -355,16 +355,25 @@ def check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan):
         raise RuntimeError("kvq input check: " + "; ".join(problems[:8]))
 
 
-def long_path():
-    """Which kernel serves long queries: "int8" (prefill_attention, reads the INT8 pages directly, needs nothing
-    outside this package) or "fa" (dequantize + vLLM's paged FlashAttention, as the reference does). The environment
-    variable KVQ_LONG_PATH picks one; by default "fa" is used where vLLM's kernel can be imported (on B200 it is the
-    faster of the two for large prefills) and "int8" otherwise."""
+# Longest query for which the INT8-page kernel is the default long path when FlashAttention is also available.
+# Measured on B200 (Qwen2.5-7B layer shape): 16 requests x 64 query tokens over 4096 keys 0.14 ms against 0.23 ms
+# for dequantize + FlashAttention; 32 x 512 over 512 keys 0.34 against 0.33 ms; 4 x 2048 over 8192 1.22 against 0.84.
+INT8_LONG_MAX_Q = int(os.environ.get("KVQ_INT8_LONG_MAX_Q", 256))
+
+
+def long_path(max_query_len=None):
+    """Which kernel serves long queries: "int8" (prefill_attention: reads the INT8 pages directly, needs nothing
+    outside this package, no temporary cache) or "fa" (dequantize + vLLM's paged FlashAttention, as the reference
+    does). The environment variable KVQ_LONG_PATH picks one; by default ("auto") the INT8-page kernel serves
+    batches whose longest query has at most INT8_LONG_MAX_Q tokens (chunked prefill, where it is the faster of
+    the two), and every batch when vLLM's kernel cannot be imported; larger prefills go to FlashAttention."""
     choice = os.environ.get("KVQ_LONG_PATH", "auto")
     if choice in ("int8", "fa"):
         return choice
     if choice != "auto":
         raise RuntimeError(f"kvq_b200: KVQ_LONG_PATH must be int8, fa or auto, got {choice!r}")
+    if max_query_len is not None and max_query_len <= INT8_LONG_MAX_Q:
+        return "int8"
     global _FA_IMPORTABLE
     if _FA_IMPORTABLE is None:
         try:
@@ -385,7 +394,7 @@ def paged_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_tabl
     if os.environ.get("KVQ_DEBUG") == "1":
         check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan)
     if plan is not None:
-        if long_path() == "int8":
+        if long_path(max_query_len) == "int8":
             prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static)
         else:
             long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, max_query_len, plan,

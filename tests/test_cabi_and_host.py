@@ -154,3 +154,32 @@ def test_vllm_surface():
     kv32 = torch.zeros(2, 16, 4, 16, dtype=torch.int8).transpose(1, 2)     # logical [nb, H, block, 2D]
     k, v = b.split_kv_cache(kv32, 8)
     assert k.shape == (2, 16, 4, 8) and k.stride() == (1024, 64, 16, 1) and v.storage_offset() == 8
+
+
+def test_long_path_policy(monkeypatch):
+    """Chunked prefill goes to the INT8-page kernel by default, an explicit choice wins, a typo is an error."""
+    monkeypatch.delenv("KVQ_LONG_PATH", raising=False)
+    assert ck.long_path(64) == "int8" and ck.long_path(ck.INT8_LONG_MAX_Q) == "int8"
+    monkeypatch.setattr(ck, "_FA_IMPORTABLE", False)
+    assert ck.long_path(4096) == "int8"            # nothing else to run it on
+    monkeypatch.setattr(ck, "_FA_IMPORTABLE", True)
+    assert ck.long_path(4096) == "fa"
+    monkeypatch.setenv("KVQ_LONG_PATH", "int8")
+    assert ck.long_path(4096) == "int8"
+    monkeypatch.setenv("KVQ_LONG_PATH", "fa")
+    assert ck.long_path(16) == "fa"
+    monkeypatch.setenv("KVQ_LONG_PATH", "flash")
+    with pytest.raises(RuntimeError, match="KVQ_LONG_PATH"):
+        ck.long_path(16)
+
+
+def test_prefill_argument_errors_are_reported_without_a_gpu():
+    lib = _native.lib()
+    assert lib.kvq_prefill_workspace_size(100) >= 256 + 101 * 4 and lib.kvq_prefill_workspace_size(-1) == 0
+    args = [1] * 9 + [0.1, 1, 16, 28, 4, 96, 16, 8] + [128] * 12 + [1, 1, 8, 1, 1024, None]
+    assert lib.kvq_int8_prefill_attention(*args) == 1 and b"head_dim" in lib.kvq_last_error()
+    args[14] = 128
+    args[12] = 30                                   # 30 q heads over 4 kv heads
+    assert lib.kvq_int8_prefill_attention(*args) == 1 and b"group" in lib.kvq_last_error()
+    args[10] = 0                                    # empty batch: silent success, like the reference's early returns
+    assert lib.kvq_int8_prefill_attention(*args) == 0

@@ -26,8 +26,9 @@ def _flash_attention_or_skip():
 
 @pytest.mark.parametrize("name,lens", [("mixed", MIXED), ("prefill", PREFILL)])
 @pytest.mark.parametrize("per_channel", [True, False])
-def test_mixed_batch_matches_oracle(name, lens, per_channel):
+def test_mixed_batch_matches_oracle(name, lens, per_channel, monkeypatch):
     _flash_attention_or_skip()
+    monkeypatch.setenv("KVQ_LONG_PATH", "fa")   # this file covers the reference's route; test_gpu_prefill.py the other
     case = workloads.paged_case(90, 28, 4, 128, *lens, per_channel=per_channel, smooth=True, q_std=3.0)
     ref = oracle_attention(case)              # implementation B for short rows, A (dequantize) for long ones
     q = case["q"].to(DEV)

@@ -181,6 +181,22 @@ int kvq_int8_prefill_attention(const void* q, const void* k_cache, const void* v
                                int v_per_channel, int min_query_len, void* workspace, size_t workspace_bytes,
                                kvq_stream_t stream);
 
+/*
+ * Calibration statistics of one step's K/V rows, folded into running totals in place: per (kv head, channel) the
+ * |x| maximum, signed maximum, signed minimum (fp32 [num_kv_heads, head_dim] each) and the sum (fp64), for K and
+ * for V, plus the number of rows counted. One fused pass in place of the eight torch reductions of the
+ * reference's capture hook `_record` (kvq/capture.py:25-44); rows with slots[t] < 0 are skipped like its
+ * `slot_mapping >= 0` mask (slots may be null: every row counts). key / value are bf16 [num_tokens, num_kv_heads,
+ * head_dim] with element strides; the caller initialises the totals (|x| max 0, max -inf, min +inf, sums 0,
+ * tokens 0). Maxima are exact; sums are accumulated to ~48 bits per block and added in fp64 with atomics, so they
+ * agree with the reference's double sum to ~1e-13 relative, not bit for bit.
+ */
+int kvq_calib_stats(const void* key, const void* value, const int64_t* slots, int64_t num_tokens, int num_kv_heads,
+                    int head_dim, int64_t key_stride_t, int64_t key_stride_h, int64_t value_stride_t,
+                    int64_t value_stride_h, float* k_absmax, float* k_max, float* k_min, double* k_sum,
+                    float* v_absmax, float* v_max, float* v_min, double* v_sum, long long* tokens,
+                    kvq_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

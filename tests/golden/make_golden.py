@@ -11,6 +11,7 @@ the inputs (small cases) or a checksum of the seeded inputs (config 0), and the 
   kvq.int8_ref.paged_static_attention        (implementation B / A, p_tile=32, short_q=8)
   kvq.ref_attn.paged_attention_ref           (bf16 golden on the unquantized cache)
   kvq.cuda_kernels.plan_long, kvq.scales.shard
+  kvq.capture._record (calibration statistics), kvq.scales.from_stats
 """
 import hashlib
 import os
@@ -26,6 +27,7 @@ if "KVQ_REF" not in os.environ:
     raise SystemExit("set KVQ_REF to a checkout of the reference project (ischencheng/int8-kvcache)")
 sys.path.insert(0, os.environ["KVQ_REF"])
 
+from kvq import capture as ref_capture  # noqa: E402
 from kvq import cuda_kernels as ref_ck  # noqa: E402
 from kvq import quant as ref_quant  # noqa: E402
 from kvq import scales as ref_scales  # noqa: E402
@@ -139,6 +141,35 @@ def save_shards():
     print("scale_shards.npz")
 
 
+def save_calib():
+    """Two steps of new K/V rows through the reference's capture hook state machine (kvq/capture.py:25-44; the
+    hook masks rows by slot >= 0 before recording, kvq/capture.py:93-96) and the scales its from_stats derives."""
+    gen = torch.Generator().manual_seed(13)
+    out = {}
+    ref_capture.STATE["stats"].clear(), ref_capture.STATE["samples"].clear()
+    rows = []
+    for i, (t, pad) in enumerate(((300, 0), (77, 5))):
+        key = (torch.randn(t + pad, 4, 128, generator=gen) * 3 + torch.randn(4, 128, generator=gen)).to(torch.bfloat16)
+        value = torch.randn(t + pad, 4, 128, generator=gen).to(torch.bfloat16)
+        slots = torch.randperm(4096, generator=gen)[:t].long()
+        slots[::11] = -1
+        valid = slots >= 0
+        ref_capture._record("layer", key[:t][valid], value[:t][valid])
+        rows.append((key[:t][valid], value[:t][valid]))
+        out[f"key{i}"], out[f"value{i}"], out[f"slots{i}"] = bits(key), bits(value), slots.numpy()
+    st = ref_capture.STATE["stats"]["layer"]
+    for f, v in st.items():
+        out["stat_" + f] = v.numpy() if torch.is_tensor(v) else np.array(v)
+    samples = {"k": torch.cat([r[0] for r in rows]).to(torch.float16), "v": torch.cat([r[1] for r in rows]).to(torch.float16)}
+    for gran, method, smooth in (("per_channel", "max", False), ("per_channel", "max", True), ("per_channel", "q0.999", True),
+                                 ("per_head", "max", True)):
+        res = ref_scales.from_stats(st, samples, gran, method, smooth)
+        for f, v in res.items():
+            out[f"scales_{gran}_{method}_{int(smooth)}_{f}"] = v.numpy()
+    np.savez_compressed(os.path.join(HERE, "calib_stats.npz"), **out)
+    print("calib_stats.npz")
+
+
 def main():
     torch.manual_seed(0)
     save_attention("attn_config0.npz", workloads.config0(), True, False, store_inputs=False, with_bf16_golden=True)
@@ -156,6 +187,7 @@ def main():
     save_quant_q()
     save_plans()
     save_shards()
+    save_calib()
 
 
 if __name__ == "__main__":

@@ -95,3 +95,30 @@ def test_round_trip_error_bound():
     s = st["k_scale"].numpy()
     y = orc.dequantize(orc.quantize(x, s), s)
     assert (np.abs(x - y) <= s / 2 + 1e-6 * (1 + np.abs(x))).all()
+
+
+def test_calibration_statistics_match_reference_hook():
+    """oracle.calib_stats and kvq_b200.scales.from_stats against the reference's capture state machine and
+    from_stats on the same two steps (fixture made by tests/golden/make_golden.py:save_calib)."""
+    import torch
+
+    from kvq_b200 import scales
+
+    fx = load_golden("calib_stats.npz")
+    batches = [(orc.bf16_bits_to_f32(fx[f"key{i}"]), orc.bf16_bits_to_f32(fx[f"value{i}"]), fx[f"slots{i}"]) for i in (0, 1)]
+    st = orc.calib_stats(batches)
+    assert st["tokens"] == int(fx["stat_tokens"])
+    for side in "kv":
+        for f in ("absmax", "max", "min"):
+            assert np.array_equal(st[f"{side}_{f}"], fx[f"stat_{side}_{f}"]), (side, f)
+        assert np.allclose(st[f"{side}_sum"], fx[f"stat_{side}_sum"], rtol=1e-12, atol=1e-9)
+    tst = {k: (torch.from_numpy(np.asarray(v)) if isinstance(v, np.ndarray) else v) for k, v in st.items()}
+    rows = [(b[0][:len(b[2])][b[2] >= 0], b[1][:len(b[2])][b[2] >= 0]) for b in batches]
+    samples = {"k": torch.from_numpy(np.concatenate([r[0] for r in rows])).to(torch.float16),
+               "v": torch.from_numpy(np.concatenate([r[1] for r in rows])).to(torch.float16)}
+    for gran, method, smooth in (("per_channel", "max", False), ("per_channel", "max", True),
+                                 ("per_channel", "q0.999", True), ("per_head", "max", True)):
+        res = scales.from_stats(tst, samples, gran, method, smooth)
+        for f, v in res.items():
+            want = fx[f"scales_{gran}_{method}_{int(smooth)}_{f}"]
+            assert np.allclose(v.numpy(), want, rtol=1e-6, atol=0), (gran, method, smooth, f)

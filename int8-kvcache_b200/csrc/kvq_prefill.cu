@@ -339,8 +339,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     {
       const __nv_bfloat16* qrow = a.q + static_cast<int64_t>(tok0 + tq) * a.q_st + static_cast<int64_t>(kvh * a.G + hg) * a.q_sh;
       const float* ksr = a.ks + kvh * (a.pc_k ? D : 1);
-      auto scaled = [&](int c, float (&f)[8]) {   // channels 8c..8c+7 of q * s_k
-        const uint4 w = __ldg(reinterpret_cast<const uint4*>(qrow) + c);
+      // 8 loads (128 bytes of the row) are in flight per round trip; the second pass finds the row in L1 / L2
+      auto scaled = [&](const uint4& w, int c, float (&f)[8]) {   // channels 8c..8c+7 of q * s_k
         const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) f[2 * e] = bf16lo(ww[e]), f[2 * e + 1] = bf16hi(ww[e]);
@@ -350,11 +350,15 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         }
       };
       float amax = 0.f;
-      if (valid) {
-#pragma unroll 4
-        for (int c = 0; c < D / 8; ++c) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / 8; c0 += 8) {
+        uint4 raw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) raw[i] = valid ? __ldg(reinterpret_cast<const uint4*>(qrow) + c0 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
           float f[8];
-          scaled(c, f);
+          scaled(raw[i], c0 + i, f);
 #pragma unroll
           for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(f[e]));
         }
@@ -365,16 +369,20 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
       const int sh = amax > 0.f ? max(-60, min(60, 15 - ex)) : 0;
       const float up = ldexpf(1.f, sh);
       c_row = a.scale_log2 * ldexpf(1.f, -sh) * (a.pc_k ? 1.f : __ldg(ksr));
-#pragma unroll 2
-      for (int c = 0; c < D / 8; ++c) {
-        uint4 o = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < D / 8; c0 += 8) {
+        uint4 raw[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) raw[i] = valid ? __ldg(reinterpret_cast<const uint4*>(qrow) + c0 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
           float f[8];
-          scaled(c, f);
-          o = make_uint4(pack_f16x2(f[0] * up, f[1] * up), pack_f16x2(f[2] * up, f[3] * up), pack_f16x2(f[4] * up, f[5] * up),
+          scaled(raw[i], c0 + i, f);   // zeros for a padding row
+          const int c = c0 + i;
+          *reinterpret_cast<uint4*>(p_q + (c >> 3) * (PF_BM * 128) + slab_off(row, c & 7)) =
+              make_uint4(pack_f16x2(f[0] * up, f[1] * up), pack_f16x2(f[2] * up, f[3] * up), pack_f16x2(f[4] * up, f[5] * up),
                          pack_f16x2(f[6] * up, f[7] * up));
         }
-        *reinterpret_cast<uint4*>(p_q + (c >> 3) * (PF_BM * 128) + slab_off(row, c & 7)) = o;
       }
     }
     fence_proxy_async();

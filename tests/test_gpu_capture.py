@@ -30,7 +30,7 @@ def test_matches_reference_hook_on_its_fixture():
     for i in (0, 1):
         capture.record("layer", bf16(fx[f"key{i}"]).to(DEV), bf16(fx[f"value{i}"]).to(DEV), torch.from_numpy(fx[f"slots{i}"]).to(DEV))
     st = capture.stats("layer")
-    check(st, {k[5:]: fx[k] for k in fx.files if k.startswith("stat_")})
+    check(st, {k[5:]: fx[k] for k in fx if k.startswith("stat_")})
     # the scales derived from the captured statistics are the reference's
     got = scales.from_stats(st, None, "per_channel", "max", True)
     for f, v in got.items():

@@ -375,6 +375,27 @@ def run_suite(args):
         fns = [(lambda i=i: ck.dequant_pages(kc, vc, ko[i], vo[i], ids[i:i + 1], zero, idx, st)) for i in range(n)]
         emit("dequant_pages_kernel", f"{P} pages x {BLOCK} x {HKV} x {D}, K and V", timed(fns), nbytes, n)
         del kc, vc, ko, vo
+    # calibration statistics of one step's new rows (the reference's hook does eight torch reductions per step)
+    from kvq_b200 import capture
+    for T in (256, 8192):
+        nbytes = T * HKV * D * 2 * 2
+        n = copies(nbytes)
+        key = torch.randn(n, T, HKV, D, device=dev).to(torch.bfloat16)
+        value = torch.randn(n, T, HKV, D, device=dev).to(torch.bfloat16)
+        capture.reset()
+        capture.MAX_SAMPLE_TOKENS, keep = 0, capture.MAX_SAMPLE_TOKENS   # statistics only: no host-side row sampling
+        fns = [(lambda i=i: capture.record("layer", key[i], value[i])) for i in range(n)]
+        us = timed(fns)
+        capture.MAX_SAMPLE_TOKENS = keep
+
+        def torch_reductions(i):
+            for x in (key[i], value[i]):
+                xf = x.float()
+                xf.abs().amax(0), xf.amax(0), xf.amin(0), xf.double().sum(0)
+
+        emit("calib_stats_kernel", f"{T} tokens x {HKV} x {D} K and V", us, nbytes, n,
+             torch_reductions_us=round(timed([(lambda i=i: torch_reductions(i)) for i in range(n)]), 2))
+        del key, value
     # standalone q quantization through the C ABI (the Python wrapper would add two allocations per call)
     lib = ck.ext()
     for T in (128, 2048):

@@ -5,8 +5,8 @@
 // torch reduction over the step's rows (eight passes over the data per layer and step). calib_stats_kernel reads
 // every row once - 16-byte loads, rows whose slot is negative skipped like the hook's `slot_mapping >= 0` mask -
 // and folds the step into the running statistics in place: maxima by integer atomics on the float bit patterns
-// (exact and order-independent), sums carried per thread as unevaluated fp32 pairs (about 48 bits) and added to the
-// fp64 totals with one atomicAdd per (block, channel).
+// (exact and order-independent), sums carried per thread as unevaluated fp32 pairs (about 48 bits), folded over the
+// block's token lanes and added to the fp64 totals with one atomicAdd per (block, channel).
 #include <algorithm>
 
 #include "kvq_common.cuh"
@@ -60,40 +60,69 @@ struct Acc {
   }
 };
 
-__global__ void __launch_bounds__(CS_THREADS) calib_stats_kernel(const CalibArgs a) {
+// Thread tid works on column group tid / lanes (8 channels) and token lane tid % lanes: the token lanes of a column
+// group are neighbouring lanes of one warp, so a block folds them with shuffles and issues one set of atomics per
+// (block, channel). Four rows are in flight per thread.
+__global__ void __launch_bounds__(CS_THREADS) calib_stats_kernel(const CalibArgs a, int lanes) {
   __shared__ int s_rows;
   const int tid = threadIdx.x;
-  const int lanes = CS_THREADS / a.groups;          // token lanes per block (>= 1; host guarantees groups <= 256)
-  const int cg = tid % a.groups, tl = tid / a.groups;
+  const int cg = tid / lanes, tl = tid - cg * lanes;
+  const bool active = cg < a.groups;
   const int h = (cg * 8) / a.D, c = (cg * 8) % a.D;
   if (tid == 0) s_rows = 0;
   __syncthreads();
   Acc k, v;
   k.init(), v.init();
   int rows = 0;
-  if (tl < lanes) {
-    for (int64_t t = static_cast<int64_t>(blockIdx.x) * lanes + tl; t < a.T; t += static_cast<int64_t>(gridDim.x) * lanes) {
-      if (a.slots && a.slots[t] < 0) continue;
-      k.add(ld_stream16(a.key + t * a.k_st + h * a.k_sh + c));
-      v.add(ld_stream16(a.value + t * a.v_st + h * a.v_sh + c));
-      ++rows;
-    }
-    if (rows) {
-      const int o = h * a.D + c;
+  if (active) {
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * lanes;
+    for (int64_t t0 = static_cast<int64_t>(blockIdx.x) * lanes + tl; t0 < a.T; t0 += 4 * stride) {
+      uint4 kw[4], vw[4];
+      bool use[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        atomicMax(reinterpret_cast<int*>(a.k_absmax + o + e), __float_as_int(k.amax[e]));   // |x| >= 0
-        atomicMax(reinterpret_cast<int*>(a.v_absmax + o + e), __float_as_int(v.amax[e]));
-        atomic_max_float(a.k_max + o + e, k.mx[e] + 0.f);   // + 0: -0.0 becomes +0.0, whose bit pattern orders correctly
-        atomic_min_float(a.k_min + o + e, k.mn[e] + 0.f);
-        atomic_max_float(a.v_max + o + e, v.mx[e] + 0.f);
-        atomic_min_float(a.v_min + o + e, v.mn[e] + 0.f);
-        atomicAdd(a.k_sum + o + e, static_cast<double>(k.hi[e]) + static_cast<double>(k.lo[e]));
-        atomicAdd(a.v_sum + o + e, static_cast<double>(v.hi[e]) + static_cast<double>(v.lo[e]));
+      for (int i = 0; i < 4; ++i) {
+        const int64_t t = t0 + i * stride;
+        use[i] = t < a.T && !(a.slots && a.slots[t] < 0);
+        if (use[i]) {
+          kw[i] = ld_stream16(a.key + t * a.k_st + h * a.k_sh + c);
+          vw[i] = ld_stream16(a.value + t * a.v_st + h * a.v_sh + c);
+        }
       }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (use[i]) k.add(kw[i]), v.add(vw[i]), ++rows;
     }
-    if (cg == 0 && rows) atomicAdd(&s_rows, rows);
   }
+  // fold the token lanes of each column group (lanes is a power of two <= 32; all 32 lanes of a warp take part)
+  const int o = h * a.D + c;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    double ks = static_cast<double>(k.hi[e]) + static_cast<double>(k.lo[e]);
+    double vs = static_cast<double>(v.hi[e]) + static_cast<double>(v.lo[e]);
+    for (int d = 1; d < lanes; d <<= 1) {
+      k.amax[e] = fmaxf(k.amax[e], __shfl_xor_sync(0xffffffffu, k.amax[e], d));
+      k.mx[e] = fmaxf(k.mx[e], __shfl_xor_sync(0xffffffffu, k.mx[e], d));
+      k.mn[e] = fminf(k.mn[e], __shfl_xor_sync(0xffffffffu, k.mn[e], d));
+      v.amax[e] = fmaxf(v.amax[e], __shfl_xor_sync(0xffffffffu, v.amax[e], d));
+      v.mx[e] = fmaxf(v.mx[e], __shfl_xor_sync(0xffffffffu, v.mx[e], d));
+      v.mn[e] = fminf(v.mn[e], __shfl_xor_sync(0xffffffffu, v.mn[e], d));
+      ks += __shfl_xor_sync(0xffffffffu, ks, d);
+      vs += __shfl_xor_sync(0xffffffffu, vs, d);
+    }
+    int any = rows;
+    for (int d = 1; d < lanes; d <<= 1) any += __shfl_xor_sync(0xffffffffu, any, d);
+    if (active && tl == 0 && any) {
+      atomicMax(reinterpret_cast<int*>(a.k_absmax + o + e), __float_as_int(k.amax[e]));   // |x| >= 0
+      atomicMax(reinterpret_cast<int*>(a.v_absmax + o + e), __float_as_int(v.amax[e]));
+      atomic_max_float(a.k_max + o + e, k.mx[e] + 0.f);   // + 0: -0.0 becomes +0.0, whose bit pattern orders correctly
+      atomic_min_float(a.k_min + o + e, k.mn[e] + 0.f);
+      atomic_max_float(a.v_max + o + e, v.mx[e] + 0.f);
+      atomic_min_float(a.v_min + o + e, v.mn[e] + 0.f);
+      atomicAdd(a.k_sum + o + e, ks);
+      atomicAdd(a.v_sum + o + e, vs);
+    }
+  }
+  if (active && cg == 0 && rows) atomicAdd(&s_rows, rows);
   __syncthreads();
   if (tid == 0 && s_rows) atomicAdd(reinterpret_cast<unsigned long long*>(a.tokens), static_cast<unsigned long long>(s_rows));
 }
@@ -124,10 +153,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_calib_stats(
   a.v_absmax = v_absmax, a.v_max = v_max, a.v_min = v_min, a.v_sum = v_sum, a.tokens = tokens;
   a.T = num_tokens, a.k_st = key_stride_t, a.k_sh = key_stride_h, a.v_st = value_stride_t, a.v_sh = value_stride_h;
   a.H = num_kv_heads, a.D = head_dim, a.groups = groups;
-  const int lanes = CS_THREADS / groups;
-  // enough blocks to fill the GPU, each with at least 8 rows per token lane so that the atomics stay a small share
-  const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(148 * 8, (num_tokens + lanes * 8 - 1) / (lanes * 8)));
-  calib_stats_kernel<<<static_cast<unsigned>(blocks), CS_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  int lanes = 1;   // token lanes per column group: the largest power of two that fits the block
+  while (lanes * 2 * groups <= CS_THREADS && lanes < 32) lanes *= 2;
+  int sms = 148;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // one block per SM at most (every block ends with one set of atomics per channel), at least 4 rows per thread
+  const int64_t blocks = std::max<int64_t>(1, std::min<int64_t>(sms, (num_tokens + lanes * 4 - 1) / (lanes * 4)));
+  calib_stats_kernel<<<static_cast<unsigned>(blocks), CS_THREADS, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a, lanes);
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
 }

@@ -118,8 +118,8 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __rest
 // ------------------------------------------------------------------------------------------------------
 // warp-specialized kernel: two m tiles per CTA share one K/V stream
 // ------------------------------------------------------------------------------------------------------
-// 13 warps: warps 0-3 and 4-7 are the softmax groups of m tile 0 and 1 (one thread per row), warps 8-11 widen the
-// int8 K/V boxes into fp16 operand tiles and issue the TMA loads, warp 12 (one lane) issues every tcgen05.mma.
+// 14 warps: warps 0-3 and 4-7 are the softmax groups of m tile 0 and 1 (one thread per row), warps 8-11 widen the
+// int8 K/V boxes into fp16 operand tiles, warp 12 (one lane) issues every tcgen05.mma, warp 13 the TMA loads.
 // The groups meet only through mbarriers. Steps are 128 keys. Per m tile the chain is S = Q.K^T -> softmax ->
 // O += P.V; the tensor core works on one tile's products while the other tile is in its softmax (the two chains run
 // half a step apart), and the converters run up to two steps ahead.
@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __rest
 // A tcgen05.mma of 128 x N x 16 with N <= 128 occupies the tensor core for ~90 cycles however small N is (measured),
 // so steps of 128 keys (N = 128 for S) halve the cost of S against 64-key steps.
 constexpr int WS_BN = 128;           // keys per step
-constexpr int WS_THREADS = 13 * 32;
+constexpr int WS_THREADS = 14 * 32;
 constexpr int WS_TMEM_COLS = 512;
 #ifdef KVQ_PF_TIMELINE
 __device__ long long g_pf_timeline[3 * 64 * 8];   // [role][step][event]
@@ -171,18 +171,23 @@ struct WsGeom {
 // int8 landing zone (TMA boxes of [16 keys][D bytes], hardware-swizzled) of WS_BN keys -> fp16 operand slabs.
 // 16 channels per item; called by the 128 converter threads.
 template <int D>
-__device__ __forceinline__ void widen_step(const uint8_t* stg, uint8_t* dst, int tid) {
-  constexpr int CPR = D / 16;
+__device__ __forceinline__ void widen_step(const uint8_t* __restrict__ stg, uint8_t* __restrict__ dst, int tid) {
+  constexpr int CPR = D / 16, N = WS_BN * CPR / 128;
+  uint4 w[N];
 #pragma unroll
-  for (int i = 0; i < WS_BN * CPR / 128; ++i) {
+  for (int i = 0; i < N; ++i) {   // every load before the first conversion
     const int idx = tid + 128 * i, key = idx / CPR, c = idx - key * CPR, kk = key & 15;
-    const uint32_t src = (key >> 4) * 16 * D + kk * D + ((D == 128 ? (c ^ (kk & 7)) : (c ^ ((kk >> 1) & 3))) << 4);
-    const uint4 w = *reinterpret_cast<const uint4*>(stg + src);
+    w[i] = *reinterpret_cast<const uint4*>(stg + (key >> 4) * 16 * D + kk * D +
+                                           ((D == 128 ? (c ^ (kk & 7)) : (c ^ ((kk >> 1) & 3))) << 4));
+  }
+#pragma unroll
+  for (int i = 0; i < N; ++i) {
+    const int idx = tid + 128 * i, key = idx / CPR, c = idx - key * CPR;
     uint4 lo, hi;
-    i8x4_to_f16x4(w.x, lo.x, lo.y);
-    i8x4_to_f16x4(w.y, lo.z, lo.w);
-    i8x4_to_f16x4(w.z, hi.x, hi.y);
-    i8x4_to_f16x4(w.w, hi.z, hi.w);
+    i8x4_to_f16x4(w[i].x, lo.x, lo.y);
+    i8x4_to_f16x4(w[i].y, lo.z, lo.w);
+    i8x4_to_f16x4(w[i].z, hi.x, hi.y);
+    i8x4_to_f16x4(w[i].w, hi.z, hi.w);
     uint8_t* slab = dst + (c >> 2) * WsGeom<D>::KV_SLAB;
     *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2)) = lo;
     *reinterpret_cast<uint4*>(slab + slab_off(key, (c & 3) * 2 + 1)) = hi;
@@ -449,14 +454,40 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
       for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
     }
   } else if (warp < 12) {
-    // ================= converters: TMA issue + int8 -> fp16 =================
+    // ================= converters: int8 -> fp16 =================
     const int ctid = tid - 256;
-    const bool issuer = warp == 8;
-    auto key_of = [&](int j) {   // first key of this lane's 16-key box of step j; boxes past the end re-read the first
+    bool ok = true;
+    for (int j = 0; j < nk && ok; ++j) {
+      const int s = j & 1;
+      if (ctid == 0) PF_TL(1, j, 0);
+      ok = ws_wait(bar(WB_STGK), j & 1, abort_flag);
+      if (ctid == 0) PF_TL(1, j, 1);
+      if (ok && j >= 2) ok = ws_wait(bar(WB_KF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (ctid == 0) PF_TL(1, j, 2);
+      widen_step<D>(p_base + Gm::OFF_SK, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
+      fence_proxy_async();
+      mbar_arrive(bar(WB_KF_READY + s));
+      mbar_arrive(bar(WB_STGK_FREE));   // the landing zone may be refilled (producer warp)
+      if (ctid == 0) PF_TL(1, j, 3);
+      ok = ws_wait(bar(WB_STGV), j & 1, abort_flag);
+      if (ctid == 0) PF_TL(1, j, 5);
+      if (ok && j >= 2) ok = ws_wait(bar(WB_VF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
+      if (!ok) break;
+      if (ctid == 0) PF_TL(1, j, 6);
+      widen_step<D>(p_base + Gm::OFF_SV, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
+      fence_proxy_async();
+      mbar_arrive(bar(WB_VF_READY + s));
+      mbar_arrive(bar(WB_STGV_FREE));
+      if (ctid == 0) PF_TL(1, j, 7);
+    }
+  } else if (warp == 13) {
+    // ================= TMA producer: lane i < 8 loads the i-th 16-key box of a step =================
+    auto key_of = [&](int j) {   // first key of this lane's box of step j; boxes past the end re-read the first
       const int n0 = j * WS_BN, n = n0 + 16 * lane;
       return n < L ? n : n0;
     };
-    auto issue = [&](bool is_k, int j, int page) {   // warp 8: lane i < 8 loads the i-th box
+    auto issue = [&](bool is_k, int j, int page) {
       const uint32_t full = bar(is_k ? WB_STGK : WB_STGV);
       if (lane == 0) mbar_expect_tx(full, Gm::STG);
       __syncwarp();
@@ -468,56 +499,25 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
                     coord(3), full);
       }
     };
-    int pg_a = 0, pg_b = 0;   // page ids (lanes 0-7 of warp 8) of the next two steps to issue
-    if (issuer) {
-      if (lane < 8 && nk > 0) pg_a = bt[key_of(0) >> a.lbs];
-      if (nk > 0) issue(true, 0, pg_a), issue(false, 0, pg_a);
-      pg_a = pg_b = 0;
-      if (lane < 8) {
-        if (nk > 1) pg_a = bt[key_of(1) >> a.lbs];
-        if (nk > 2) pg_b = bt[key_of(2) >> a.lbs];
-      }
+    int pg_a = 0, pg_b = 0;   // page ids (lanes 0-7) of the next two steps to issue
+    if (lane < 8 && nk > 0) pg_a = bt[key_of(0) >> a.lbs];
+    if (nk > 0) issue(true, 0, pg_a), issue(false, 0, pg_a);
+    pg_a = pg_b = 0;
+    if (lane < 8) {
+      if (nk > 1) pg_a = bt[key_of(1) >> a.lbs];
+      if (nk > 2) pg_b = bt[key_of(2) >> a.lbs];
     }
     bool ok = true;
-    for (int j = 0; j < nk && ok; ++j) {
-      const int s = j & 1;
-      // pg_a belongs to step j + 1 (issued below), pg_b to step j + 2
-      if (ctid == 0) PF_TL(1, j, 0);
-      ok = ws_wait(bar(WB_STGK), j & 1, abort_flag);
-      if (ctid == 0) PF_TL(1, j, 1);
-      if (ok && j >= 2) ok = ws_wait(bar(WB_KF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
-      if (!ok) break;
-      if (ctid == 0) PF_TL(1, j, 2);
-      widen_step<D>(p_base + Gm::OFF_SK, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
-      fence_proxy_async();
-      mbar_arrive(bar(WB_KF_READY + s));
-      mbar_arrive(bar(WB_STGK_FREE));
-      if (ctid == 0) PF_TL(1, j, 3);
-      if (issuer && j + 1 < nk) {   // every converter has left the landing zone before it is refilled
-        ok = ws_wait(bar(WB_STGK_FREE), j & 1, abort_flag);
-        if (ok) issue(true, j + 1, pg_a);
-      }
-      if (ctid == 0) PF_TL(1, j, 4);
-      ok = ok && ws_wait(bar(WB_STGV), j & 1, abort_flag);
-      if (ctid == 0) PF_TL(1, j, 5);
-      if (ok && j >= 2) ok = ws_wait(bar(WB_VF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
-      if (!ok) break;
-      if (ctid == 0) PF_TL(1, j, 6);
-      widen_step<D>(p_base + Gm::OFF_SV, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
-      fence_proxy_async();
-      mbar_arrive(bar(WB_VF_READY + s));
-      mbar_arrive(bar(WB_STGV_FREE));
-      if (ctid == 0) PF_TL(1, j, 7);
-      if (issuer) {
-        if (j + 1 < nk) {
-          ok = ws_wait(bar(WB_STGV_FREE), j & 1, abort_flag);
-          if (ok) issue(false, j + 1, pg_a);
-        }
-        pg_a = pg_b;
-        pg_b = (lane < 8 && j + 3 < nk) ? bt[key_of(j + 3) >> a.lbs] : 0;
-      }
+    for (int j = 0; j + 1 < nk && ok; ++j) {
+      // pg_a belongs to step j + 1, pg_b to step j + 2; a landing zone is refilled once every converter has read it
+      ok = ws_wait(bar(WB_STGK_FREE), j & 1, abort_flag);
+      if (ok) issue(true, j + 1, pg_a);
+      ok = ok && ws_wait(bar(WB_STGV_FREE), j & 1, abort_flag);
+      if (ok) issue(false, j + 1, pg_a);
+      pg_a = pg_b;
+      pg_b = (lane < 8 && j + 3 < nk) ? bt[key_of(j + 3) >> a.lbs] : 0;
     }
-  } else if (lane == 0) {
+  } else if (warp == 12 && lane == 0) {
     // ================= tensor-core issue (one thread) =================
     bool ok = ws_wait_thread(bar(WB_Q_READY), 0, abort_flag);
     // Descriptors differ only in their 14-bit start-address field (address >> 4): one base per operand, the

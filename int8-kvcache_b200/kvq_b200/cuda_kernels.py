@@ -356,8 +356,8 @@ def check_inputs(q, k_cache, cu_seqlens_q, seq_lens, block_table, plan):
 
 
 # Longest query for which the INT8-page kernel is the default long path when FlashAttention is also available.
-# Measured on B200 (Qwen2.5-7B layer shape): 16 requests x 64 query tokens over 4096 keys 0.14 ms against 0.23 ms
-# for dequantize + FlashAttention; 32 x 512 over 512 keys 0.34 against 0.33 ms; 4 x 2048 over 8192 1.22 against 0.84.
+# Measured on B200 (Qwen2.5-7B layer shape): 16 requests x 64 query tokens over 4096 keys 0.13 ms against 0.23 ms
+# for dequantize + FlashAttention; 32 x 512 over 512 keys 0.33 against 0.32 ms; 4 x 2048 over 8192 1.10 against 0.84.
 INT8_LONG_MAX_Q = int(os.environ.get("KVQ_INT8_LONG_MAX_Q", 256))
 
 

@@ -308,6 +308,36 @@ __device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, flo
   }
 }
 
+// Packed fp32 pairs (sm_100: add / mul / fma .f32x2 are two IEEE operations in one instruction).
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pk2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// score() for two dots of one row: fp32(dot * (hi + lo)) with one rounding each. nhi = -hi (packed pair).
+__device__ __forceinline__ void score2(int d0, int d1, f32x2 hi, f32x2 nhi, f32x2 lo, float& s0, float& s1) {
+  const f32x2 d = pk2(static_cast<float>(d0), static_cast<float>(d1));
+  const f32x2 pn = mul2(d, nhi);                       // -(d * hi), rounded
+  upk2(sub2(fma2(d, lo, fma2(d, hi, pn)), pn), s0, s1);   // p + (d * lo + (d * hi - p))
+}
+
 // Per-warp state of one m tile: q fragments, score scales, causal limits, running softmax statistics, output.
 template <int D, bool ROWS16>
 struct TileState {
@@ -341,18 +371,23 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   const bool need_mask = n_base + CHUNK > lim_all;
   float p0[8], p1[8];
   float mx0 = -INFINITY, mx1 = -INFINITY;
+  const f32x2 hi0 = pk2(s.ch0, s.ch0), nhi0 = pk2(-s.ch0, -s.ch0), lo0 = pk2(s.cl0, s.cl0);
+  const f32x2 hi1 = pk2(s.ch1, s.ch1), nhi1 = pk2(-s.ch1, -s.ch1), lo1 = pk2(s.cl1, s.cl1);
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
+  for (int j = 0; j < 4; ++j) {
+    score2(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
+    if (ROWS16) score2(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int n = n_base + 8 * j + 2 * t + e;
-      p0[2 * j + e] = (!need_mask || n < s.lim0) ? score(sacc[j][e], s.ch0, s.cl0) : -INFINITY;
+      if (need_mask && n >= s.lim0) p0[2 * j + e] = -INFINITY;
       mx0 = fmaxf(mx0, p0[2 * j + e]);
       if (ROWS16) {
-        p1[2 * j + e] = (!need_mask || n < s.lim1) ? score(sacc[j][2 + e], s.ch1, s.cl1) : -INFINITY;
+        if (need_mask && n >= s.lim1) p1[2 * j + e] = -INFINITY;
         mx1 = fmaxf(mx1, p1[2 * j + e]);
       }
     }
+  }
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
   const float mn0 = fmaxf(s.m0, mx0), nb0 = -mn0 * LOG2E;
@@ -362,10 +397,17 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   const float ps0 = fmaxf(ex2(fmaf(mx0, LOG2E, nb0)) * (1.f / 127.f), 1e-30f);
   const float ri0 = __frcp_rn(ps0);
   int q0[8], qs0 = 0;
+  const f32x2 l2e = pk2(LOG2E, LOG2E);
+  {
+    const f32x2 nb = pk2(nb0, nb0), ri = pk2(ri0, ri0);
 #pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    q0[k] = min(__float2int_rn(ex2(fmaf(p0[k], LOG2E, nb0)) * ri0), 127);
-    qs0 += q0[k];
+    for (int k = 0; k < 8; k += 2) {
+      float x0, x1;
+      upk2(fma2(pk2(p0[k], p0[k + 1]), l2e, nb), x0, x1);
+      upk2(mul2(pk2(ex2(x0), ex2(x1)), ri), x0, x1);
+      q0[k] = min(__float2int_rn(x0), 127), q0[k + 1] = min(__float2int_rn(x1), 127);
+      qs0 += q0[k] + q0[k + 1];
+    }
   }
   float al1 = 1.f, ps1 = 0.f;
   int q1[8], qs1 = 0;
@@ -376,10 +418,14 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
     al1 = (s.m1 == mn1) ? 1.f : ex2(fmaf(s.m1, LOG2E, nb1));
     ps1 = fmaxf(ex2(fmaf(mx1, LOG2E, nb1)) * (1.f / 127.f), 1e-30f);
     const float ri1 = __frcp_rn(ps1);
+    const f32x2 nb = pk2(nb1, nb1), ri = pk2(ri1, ri1);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      q1[k] = min(__float2int_rn(ex2(fmaf(p1[k], LOG2E, nb1)) * ri1), 127);
-      qs1 += q1[k];
+    for (int k = 0; k < 8; k += 2) {
+      float x0, x1;
+      upk2(fma2(pk2(p1[k], p1[k + 1]), l2e, nb), x0, x1);
+      upk2(mul2(pk2(ex2(x0), ex2(x1)), ri), x0, x1);
+      q1[k] = min(__float2int_rn(x0), 127), q1[k + 1] = min(__float2int_rn(x1), 127);
+      qs1 += q1[k] + q1[k + 1];
     }
     s.m1 = mn1;
     qs0 |= qs1 << 16;  // both row sums (each < 2^13) through one pair of shuffles
@@ -399,6 +445,7 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   pa[1] = ROWS16 ? pack4(q1[0], q1[1], q1[2], q1[3]) : 0u;
   pa[3] = ROWS16 ? pack4(q1[4], q1[5], q1[6], q1[7]) : 0u;
 
+  const f32x2 al0_2 = pk2(al0, al0), ps0_2 = pk2(ps0, ps0), al1_2 = pk2(al1, al1), ps1_2 = pk2(ps1, ps1);
   // O += P.V: 16 channels (two n-tiles) per transposing ldmatrix
 #pragma unroll
   for (int jp = 0; jp < NT / 2; ++jp) {
@@ -409,12 +456,10 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
       int pacc[4] = {0, 0, 0, 0};
       mma_s8(pacc, pa, b[h2], b[2 + h2]);
       float* o = s.acc[2 * jp + h2];
-      o[0] = o[0] * al0 + static_cast<float>(pacc[0]) * ps0;
-      o[1] = o[1] * al0 + static_cast<float>(pacc[1]) * ps0;
-      if (ROWS16) {
-        o[2] = o[2] * al1 + static_cast<float>(pacc[2]) * ps1;
-        o[3] = o[3] * al1 + static_cast<float>(pacc[3]) * ps1;
-      }
+      // (o0, o1) = (x0, x1) * ps + (o0, o1) * al
+      upk2(fma2(pk2(static_cast<float>(pacc[0]), static_cast<float>(pacc[1])), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
+      if (ROWS16)
+        upk2(fma2(pk2(static_cast<float>(pacc[2]), static_cast<float>(pacc[3])), ps1_2, mul2(pk2(o[2], o[3]), al1_2)), o[2], o[3]);
     }
   }
 }

@@ -110,15 +110,6 @@ __device__ __forceinline__ ff ff_mul(ff a, ff b) {
 }
 __device__ __forceinline__ ff ff_max(ff a, ff b) { return (b.hi > a.hi || (b.hi == a.hi && b.lo > a.lo)) ? b : a; }
 
-// fp32(dot * c) for c = hi + lo: the product is formed to ~48 bits and rounded once, like the reference's
-// float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100 that moves
-// P = exp(score - max) by 1e-5 and flips its int8 quantization far more often than the reference's own noise.
-__device__ __forceinline__ float score(int dot, float hi, float lo) {
-  const float d = static_cast<float>(dot);  // |dot| < 2^24: exact
-  const float p = d * hi;
-  return p + fmaf(d, lo, fmaf(d, hi, -p));
-}
-
 // Byte offset of (key row tau, 16-byte column c16) inside a TMA-written tile of D-byte rows. The tile base
 // is 1024-byte aligned; TMA's 128B swizzle XORs address bits [4:6] with bits [7:9] (64B: bits [4:5] with [7:8]).
 // A tile is two TMA boxes of 16 keys; a box holds hs heads per key ([key][head][D], hs = 1 except in head-group
@@ -308,6 +299,15 @@ __device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, flo
   }
 }
 
+// Four ints -> four int8 bytes (a lowest), each saturated to [-128, 127]: two saturating packs. cvt.pack puts its
+// first source in bits 15:8, the second in bits 7:0 and the low half of the third operand in bits 31:16.
+__device__ __forceinline__ uint32_t pack4_sat8(int a, int b, int c, int d) {
+  uint32_t hi, r;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi) : "r"(d), "r"(c), "r"(0));
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(b), "r"(a), "r"(hi));
+  return r;
+}
+
 // Packed fp32 pairs (sm_100: add / mul / fma .f32x2 are two IEEE operations in one instruction).
 using f32x2 = unsigned long long;
 __device__ __forceinline__ f32x2 pk2(float a, float b) {
@@ -331,7 +331,10 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
-// score() for two dots of one row: fp32(dot * (hi + lo)) with one rounding each. nhi = -hi (packed pair).
+// Scores of two dots of one row: fp32(dot * c) for c = hi + lo. The product is formed to ~48 bits and rounded once,
+// like the reference's float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100
+// that moves P = exp(score - max) by 1e-5 and flips its int8 quantization far more often than the reference's own
+// noise. nhi = -hi (packed pair).
 __device__ __forceinline__ void score2(int d0, int d1, f32x2 hi, f32x2 nhi, f32x2 lo, float& s0, float& s1) {
   const f32x2 d = pk2(static_cast<float>(d0), static_cast<float>(d1));
   const f32x2 pn = mul2(d, nhi);                       // -(d * hi), rounded
@@ -396,37 +399,34 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   // the tile maximum of P is pexp(mx): the same instructions compute every P below, and they are monotonic
   const float ps0 = fmaxf(ex2(fmaf(mx0, LOG2E, nb0)) * (1.f / 127.f), 1e-30f);
   const float ri0 = __frcp_rn(ps0);
-  int q0[8], qs0 = 0;
+  // P = min(rint(exp2(.) / ps), 127) as int8: round to int, then saturating packs (cvt.pack.sat) build the A operand of
+  // the PV mma directly (k slots 4t..4t+3 <- keys {2t, 2t+1, 8+2t, 9+2t}, slots 16+.. <- +16) and a byte dot product
+  // with ones gives the row sum.
   const f32x2 l2e = pk2(LOG2E, LOG2E);
-  {
-    const f32x2 nb = pk2(nb0, nb0), ri = pk2(ri0, ri0);
+  auto quant8 = [&](const float (&p)[8], float nbx, float rix, uint32_t& lo4, uint32_t& hi4) {
+    const f32x2 nb = pk2(nbx, nbx), ri = pk2(rix, rix);
+    int q[8];
 #pragma unroll
     for (int k = 0; k < 8; k += 2) {
       float x0, x1;
-      upk2(fma2(pk2(p0[k], p0[k + 1]), l2e, nb), x0, x1);
+      upk2(fma2(pk2(p[k], p[k + 1]), l2e, nb), x0, x1);
       upk2(mul2(pk2(ex2(x0), ex2(x1)), ri), x0, x1);
-      q0[k] = min(__float2int_rn(x0), 127), q0[k + 1] = min(__float2int_rn(x1), 127);
-      qs0 += q0[k] + q0[k + 1];
+      q[k] = __float2int_rn(x0), q[k + 1] = __float2int_rn(x1);
     }
-  }
+    lo4 = pack4_sat8(q[0], q[1], q[2], q[3]);
+    hi4 = pack4_sat8(q[4], q[5], q[6], q[7]);
+    return __dp4a(static_cast<int>(lo4), 0x01010101, __dp4a(static_cast<int>(hi4), 0x01010101, 0));
+  };
+  uint32_t pa[4] = {0u, 0u, 0u, 0u};
+  int qs0 = quant8(p0, nb0, ri0, pa[0], pa[2]);
   float al1 = 1.f, ps1 = 0.f;
-  int q1[8], qs1 = 0;
   if (ROWS16) {
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn1 = fmaxf(s.m1, mx1), nb1 = -mn1 * LOG2E;
     al1 = (s.m1 == mn1) ? 1.f : ex2(fmaf(s.m1, LOG2E, nb1));
     ps1 = fmaxf(ex2(fmaf(mx1, LOG2E, nb1)) * (1.f / 127.f), 1e-30f);
-    const float ri1 = __frcp_rn(ps1);
-    const f32x2 nb = pk2(nb1, nb1), ri = pk2(ri1, ri1);
-#pragma unroll
-    for (int k = 0; k < 8; k += 2) {
-      float x0, x1;
-      upk2(fma2(pk2(p1[k], p1[k + 1]), l2e, nb), x0, x1);
-      upk2(mul2(pk2(ex2(x0), ex2(x1)), ri), x0, x1);
-      q1[k] = min(__float2int_rn(x0), 127), q1[k + 1] = min(__float2int_rn(x1), 127);
-      qs1 += q1[k] + q1[k + 1];
-    }
+    const int qs1 = quant8(p1, nb1, __frcp_rn(ps1), pa[1], pa[3]);
     s.m1 = mn1;
     qs0 |= qs1 << 16;  // both row sums (each < 2^13) through one pair of shuffles
   }
@@ -438,12 +438,6 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
     qs0 &= 0xffff;
   }
   s.l0 = s.l0 * al0 + static_cast<float>(qs0) * ps0;
-  // P as the A operand of the PV mma: k slots 4t..4t+3 <- keys {2t, 2t+1, 8+2t, 9+2t}, slots 16+.. <- +16
-  uint32_t pa[4];
-  pa[0] = pack4(q0[0], q0[1], q0[2], q0[3]);
-  pa[2] = pack4(q0[4], q0[5], q0[6], q0[7]);
-  pa[1] = ROWS16 ? pack4(q1[0], q1[1], q1[2], q1[3]) : 0u;
-  pa[3] = ROWS16 ? pack4(q1[4], q1[5], q1[6], q1[7]) : 0u;
 
   const f32x2 al0_2 = pk2(al0, al0), ps0_2 = pk2(ps0, ps0), al1_2 = pk2(al1, al1), ps1_2 = pk2(ps1, ps1);
   // O += P.V: 16 channels (two n-tiles) per transposing ldmatrix

@@ -74,6 +74,19 @@ __device__ __forceinline__ void i8x4_to_f16x4(uint32_t w, uint32_t& lo, uint32_t
   lo = *reinterpret_cast<const uint32_t*>(&x);
   hi = *reinterpret_cast<const uint32_t*>(&y);
 }
+// Packed fp32 pairs (sm_100: fma.rn.f32x2 is two IEEE operations in one instruction).
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pk2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& a, float& b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -387,7 +400,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
       // (chunk i reads S columns [32 i, 32 i + 32) and then writes P columns [16 i, 16 i + 16): never ahead of a
       // read). P.V may start on the first 64 keys while the last 64 are still being computed.
       {
-        const float nm = -m_ref;
+        const f32x2 c2 = pk2(c_row, c_row), nm2 = pk2(-m_ref, -m_ref);
         float ls = 0.f;
 #pragma unroll 1
         for (int c = 0; c < WS_BN; c += 32) {
@@ -397,8 +410,9 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float p0 = ex2(fmaf(__uint_as_float(sr[2 * i]), c_row, nm));
-            float p1 = ex2(fmaf(__uint_as_float(sr[2 * i + 1]), c_row, nm));
+            float x0, x1, p0, p1;
+            upk2(fma2(pk2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), c2, nm2), x0, x1);
+            p0 = ex2(x0), p1 = ex2(x1);
             if (masked) {
               p0 = n_base + c + 2 * i < lim ? p0 : 0.f;
               p1 = n_base + c + 2 * i + 1 < lim ? p1 : 0.f;

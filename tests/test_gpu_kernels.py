@@ -167,6 +167,8 @@ def test_attention_config0_golden():
     out = run_decode(workloads.config0())
     assert_close(fx["ref_out"], out, "config0", strict=True)
     assert orc.compare(fx["bf16_golden"], out)["rel_l2"] < 0.05
+    # beyond the tolerance: the bf16 output is the bf16 rounding of the reference's fp32 result almost everywhere
+    assert (orc.round_to_bf16(fx["ref_out"]) == out).mean() > 0.999
 
 
 def test_mixed_batch_leaves_long_requests_alone():

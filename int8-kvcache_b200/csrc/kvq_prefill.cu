@@ -87,6 +87,11 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   const __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&h);
@@ -408,17 +413,31 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
           tmem_ld32(t_s + c, sr);
           tmem_wait_ld();
           uint32_t w[16];
+          f32x2 ls2 = pk2(0.f, 0.f);
+          if (!masked) {   // every step but the last ones of a row
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            float x0, x1, p0, p1;
-            upk2(fma2(pk2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), c2, nm2), x0, x1);
-            p0 = ex2(x0), p1 = ex2(x1);
-            if (masked) {
-              p0 = n_base + c + 2 * i < lim ? p0 : 0.f;
-              p1 = n_base + c + 2 * i + 1 < lim ? p1 : 0.f;
+            for (int i = 0; i < 16; ++i) {
+              float x0, x1;
+              upk2(fma2(pk2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), c2, nm2), x0, x1);
+              const float p0 = ex2(x0), p1 = ex2(x1);
+              ls2 = add2(ls2, pk2(p0, p1));
+              w[i] = pack_f16x2(p0, p1);
             }
-            ls += p0 + p1;
-            w[i] = pack_f16x2(p0, p1);
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float x0, x1;
+              upk2(fma2(pk2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1])), c2, nm2), x0, x1);
+              const float p0 = n_base + c + 2 * i < lim ? ex2(x0) : 0.f;
+              const float p1 = n_base + c + 2 * i + 1 < lim ? ex2(x1) : 0.f;
+              ls2 = add2(ls2, pk2(p0, p1));
+              w[i] = pack_f16x2(p0, p1);
+            }
+          }
+          {
+            float a0, a1;
+            upk2(ls2, a0, a1);
+            ls += a0 + a1;
           }
           tmem_st16(t_s + (c >> 1), w);
           if (c & 32) {   // 64 keys of P complete

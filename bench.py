@@ -11,8 +11,15 @@ microseconds per call and decode tokens/s (requests per step / time) are reporte
 Requests are sharded over GPUs (each rank owns its requests and their pages): weak scaling, no collective in
 the data path.
 
-One JSON line is printed by rank 0. `--impl reference` times the CPU restatement of the reference's PyTorch
-implementation B (oracle/) on the host cores instead, on a bounded sample of the same workload.
+One JSON line is printed by rank 0. Beside the headline it carries: `roofline` (the main kernel against the
+measured HBM copy rate), `e2e` (the same step from pinned host buffers through the public API), `output_check` (8 of
+the timed batch's requests recomputed by the CPU oracle after the timed loop), `strong` (the fixed 128 x 32k layer
+sharded 128/N requests per GPU with the NCCL all-gather of the outputs inside the timed step), `model_step` (the
+28-layer decode step of benchmark configuration 4 with 512/N requests per GPU) and, at N = 1, `cpu_baseline`.
+
+`--impl reference` times the reference's own PyTorch implementation B on the host cores instead (oracle/_ref, staged
+by oracle/build_ref.py; the numpy restatement in oracle/ where that is absent), each step a bounded sample of the
+same workload.
 """
 import argparse
 import json
@@ -47,7 +54,7 @@ def peaks():
     if os.path.exists(path):
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+    return 6650.0, "fallback (no MEASURED_PEAKS.json next to bench.py)"
 
 
 class ClockSampler:
@@ -93,7 +100,10 @@ class ClockSampler:
 # --------------------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference's implementation B on the host cores
 # --------------------------------------------------------------------------------------------------------
-def cpu_sample_case(requests, seed=1002):
+CPU_SAMPLE_REQUESTS = 8     # requests of the 128 that one CPU step computes (both CPU legs use this sample)
+
+
+def cpu_sample_case(requests=CPU_SAMPLE_REQUESTS, seed=1002):
     """`requests` requests of the benchmark workload (same shapes and distributions), generated on the CPU."""
     from kvq_b200 import workloads
 
@@ -101,60 +111,135 @@ def cpu_sample_case(requests, seed=1002):
                                 num_blocks=requests * (CTX // BLOCK) + 1)
 
 
-def cpu_run(case):
-    from oracle import kvq_oracle as orc
+def cpu_runner(case):
+    """(fn, kind, description): fn() computes the sample once on the host cores and returns seconds.
+    kind "reference": the reference's own PyTorch implementation B (kvq/int8_ref.py paged_static_attention with
+    Cfg(p_tile=32), byte-compiled into oracle/_ref by oracle/build_ref.py), torch threads = all cores.
+    kind "port": the numpy restatement in oracle/kvq_oracle.py, where oracle/_ref is absent."""
+    from oracle import build_ref
 
     st = case["static"]
+    mods = build_ref.load()
+    if mods is not None:
+        _, _, int8_ref = mods
+        torch.set_num_threads(os.cpu_count())
+        fn = int8_ref.paged_static_attention(int8_ref.Cfg(p_tile=32), st, cache_is_int8=True, short_q=8)
+        args = (case["q"].float(), case["kq"], case["vq"], case["cu_seqlens_q"], case["seq_lens"], case["block_table"],
+                case["softmax_scale"])
+
+        def run():
+            t0 = time.perf_counter()
+            fn(*args)
+            return time.perf_counter() - t0
+
+        return run, "reference", ("the reference's PyTorch implementation B (kvq/int8_ref.py, p_tile 32) from oracle/_ref, "
+                                  f"torch threads = {torch.get_num_threads()}")
+    from oracle import kvq_oracle as orc
+
     args = (case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(), case["cu_seqlens_q"].numpy(),
             case["seq_lens"].numpy(), case["block_table"].numpy(), case["softmax_scale"], st["k_scale"].numpy(),
             st["v_scale"].numpy())
-    t0 = time.perf_counter()
-    orc.paged_static_attention(*args, short_q=8, p_tile=32)
-    return time.perf_counter() - t0
+
+    def run():
+        t0 = time.perf_counter()
+        orc.paged_static_attention(*args, short_q=8, p_tile=32)
+        return time.perf_counter() - t0
+
+    return run, "port", "numpy restatement of kvq/int8_ref.py implementation B (oracle/kvq_oracle.py; oracle/_ref absent)"
 
 
-def cpu_baseline(requests=16, repeats=3):
-    case = cpu_sample_case(requests)
-    cpu_run(case)                                   # warm-up (BLAS thread pool, page faults)
-    t = min(cpu_run(case) for _ in range(repeats))
-    return {"value": kv_bytes([CTX] * requests) / t / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{requests} of the {BATCH} requests (x{CTX} context), numpy port of kvq/int8_ref.py "
-                      f"implementation B, BLAS threads = all cores, best of {repeats}",
+def cpu_baseline(repeats=5):
+    """The CPU leg of the GPU arm's line: same sample and same statistic (mean) as `--impl reference`."""
+    case = cpu_sample_case()
+    run, kind, what = cpu_runner(case)
+    run()                                   # warm-up (thread pool, page faults)
+    t = float(np.mean([run() for _ in range(repeats)]))
+    return {"value": kv_bytes([CTX] * CPU_SAMPLE_REQUESTS) / t / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": kind,
+            "sample": f"{CPU_SAMPLE_REQUESTS} of the {BATCH} requests (x{CTX} context) per step, mean of {repeats} steps; {what}",
             "seconds_per_sample": t}
 
 
+REFERENCE_ARM_BUDGET_S = 240.0   # wall-time bound of the whole CPU arm
+
+
 def run_reference_arm(args, rank):
+    """--steps / --warmup are honoured; only if the run would exceed REFERENCE_ARM_BUDGET_S of wall time are the
+    timed steps cut short, and the line then says how many ran."""
     if rank != 0:
         return
-    requests = 8
+    requests = CPU_SAMPLE_REQUESTS
     case = cpu_sample_case(requests)
+    run, kind, what = cpu_runner(case)
+    t_begin = time.perf_counter()
     for _ in range(args.warmup):
-        cpu_run(case)
-    times = [cpu_run(case) for _ in range(args.steps)]
+        run()
+    times = []
+    for _ in range(args.steps):
+        times.append(run())
+        if time.perf_counter() - t_begin > REFERENCE_ARM_BUDGET_S and len(times) >= 3:
+            break
     t = sum(times) / len(times)
     value = kv_bytes([CTX] * requests) / t / 1e9
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+    sample = f"each step = {requests} of the {BATCH} requests (x{CTX} context) on the host CPU; {what}"
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
             "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int8 (int32 accumulate), fp32 softmax", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "sample": f"each step = {requests} of the {BATCH} requests on the host CPU"},
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-                             "sample": f"{requests} requests x {CTX} context per step; oracle/kvq_oracle.py (numpy "
-                                       "restatement of kvq/int8_ref.py implementation B; the reference is Python and "
-                                       "is not present on the GPU box)"},
+            "config": {"workload": WORKLOAD, "sample": sample},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    if len(times) < args.steps:
+        line["steps_requested"] = args.steps
+        line["steps_note"] = f"stopped after {len(times)} steps: wall-time bound of {REFERENCE_ARM_BUDGET_S:.0f} s for the CPU arm"
     print(json.dumps(line), flush=True)
 
 
 # --------------------------------------------------------------------------------------------------------
 # GPU arm
 # --------------------------------------------------------------------------------------------------------
+def output_check(case, out_ref, ck, rank, picks=8):
+    """After the timed loop: `picks` requests of the timed batch (first, last and a seeded sample) are run once more
+    through decode_attention as a batch of their own and recomputed by the CPU oracle from the very pages the
+    kernel read (pulled from HBM through the block table). Bar: max-abs 1e-2, mean-abs 1e-3 against the fp32 oracle."""
+    from oracle import kvq_oracle as orc
+
+    n_req = len(case["q_lens"])
+    rng = np.random.default_rng(1002)
+    sel = sorted({0, n_req - 1, *rng.choice(n_req, size=min(picks, n_req), replace=False).tolist()})[:picks]
+    q_len = case["q_lens"][0]
+    cu_all = case["cu_seqlens_q"].cpu().numpy()
+    seq = case["seq_lens"].cpu().numpy()
+    rows = np.concatenate([np.arange(cu_all[r], cu_all[r + 1]) for r in sel])
+    idx = torch.as_tensor(sel, device=case["q"].device)
+    q_sel = case["q"][torch.as_tensor(rows, device=case["q"].device)].contiguous()
+    out_sel = torch.zeros_like(q_sel)
+    cu_sel = torch.arange(0, (len(sel) + 1) * q_len, q_len, dtype=torch.int32, device=q_sel.device)
+    ck.decode_attention(q_sel, case["kq"], case["vq"], out_sel, cu_sel, case["seq_lens"][idx].contiguous(),
+                        case["block_table"][idx].contiguous(), case["softmax_scale"], case["static"], max_query_len=q_len)
+    torch.cuda.synchronize()
+    got = out_sel.float().cpu().numpy()
+    st = {k: v.cpu().numpy() for k, v in case["static"].items()}
+    bs = case["kq"].shape[1]
+    worst = {"max_abs": 0.0, "mean_abs": 0.0}
+    for i, r in enumerate(sel):
+        L = int(seq[r])
+        pages = case["block_table"][r, :(L + bs - 1) // bs].long()
+        k_r, v_r = case["kq"][pages].cpu().numpy(), case["vq"][pages].cpu().numpy()      # [pages, bs, H, D]
+        bt_r = np.arange(k_r.shape[0], dtype=np.int32)[None]
+        ref = orc.paged_static_attention(q_sel[i * q_len:(i + 1) * q_len].float().cpu().numpy(), k_r, v_r,
+                                         np.array([0, q_len]), np.array([L]), bt_r, case["softmax_scale"],
+                                         st["k_scale"], st["v_scale"])
+        err = orc.compare(ref, got[i * q_len:(i + 1) * q_len])
+        worst = {k: max(worst[k], err[k]) for k in worst}
+    ok = worst["max_abs"] <= 1e-2 and worst["mean_abs"] <= 1e-3
+    if not ok:
+        raise SystemExit(f"bench.py: output check failed on requests {sel}: {worst}")
+    return {"requests": sel, "max_abs": worst["max_abs"], "mean_abs_worst_request": worst["mean_abs"],
+            "bar": "max-abs 1e-2, mean-abs 1e-3 vs the fp32 CPU oracle", "ok": True}
+
+
 def run_ours(args, rank, world, local_rank):
-    torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    from kvq_b200 import _native
     from kvq_b200 import cuda_kernels as ck
     from kvq_b200 import workloads
 
@@ -260,14 +345,41 @@ def run_ours(args, rank, world, local_rank):
     sync_all()
     e2e_ms = e_start.elapsed_time(e_stop)
 
+    # ---- strong scaling: the FIXED headline layer (128 requests in total) sharded 128 / N requests per GPU, with the
+    #      NCCL all-gather of every rank's output rows inside the timed step ----
+    strong = None
+    if (batch, ctx, q_len) == (BATCH, CTX, 1) and BATCH % world == 0:
+        from kvq_b200 import sharding
+
+        n = BATCH // world
+        q_n, out_n, cu_n, sl_n, bt_n = q[:n], out[:n], cu[:n + 1], sl[:n], bt[:n]
+        gathered = torch.empty(BATCH, HQ, D, dtype=out.dtype, device=dev) if world > 1 else None
+
+        def strong_step():
+            ck.decode_attention(q_n, kq, vq, out_n, cu_n, sl_n, bt_n, scale, st, max_query_len=1)
+            if world > 1:
+                sharding.gather_outputs(out_n, [n] * world, out=gathered)
+
+        for _ in range(3):
+            strong_step()
+        sync_all()
+        s_start, s_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_start.record()
+        for _ in range(args.steps):
+            strong_step()
+        s_stop.record()
+        sync_all()
+        strong = s_start.elapsed_time(s_stop)
+
+    # ---- output check: a seeded subset of the timed batch recomputed by the CPU oracle ----
+    check = output_check(case, out_ref=None, ck=ck, rank=rank) if rank == 0 and not args.no_check else None
+
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms], device=dev)
+        t = torch.tensor([elapsed_ms, e2e_ms, strong or 0.0], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+        elapsed_ms, e2e_ms, strong = float(t[0]), float(t[1]), (float(t[2]) if strong is not None else None)
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     ms_per_step = elapsed_ms / args.steps
     value = world * bytes_per_step / (ms_per_step * 1e-3) / 1e9
@@ -281,7 +393,9 @@ def run_ours(args, rank, world, local_rank):
         "vs_baseline_note": "reference's own CUDA kernel on H100, 2439 GB/s (published; no B200 number exists)",
         "dtype": "int8 (int32 accumulate), fp32 softmax", "data": "synthetic",
         "config": {"workload": WORKLOAD if (batch, ctx) == (BATCH, CTX) else f"decode_attention {batch}x{ctx} per GPU (non-headline size)", "global_requests": batch * world, "sharding": f"requests over {world} GPU(s)",
-                   "l2": "inputs (4.3 GB of KV per step) are larger than L2", "timed_call": "cuda_kernels.decode_attention"},
+                   "l2": "inputs (4.3 GB of KV per step) are larger than L2", "timed_call": "cuda_kernels.decode_attention",
+                   "scales": "analytic 4.5 sigma_c / 127 per (kv head, channel) instead of absmax / 127 over the generated "
+                             "pool (no bf16 copy of the 4.3 GB pool is ever held); same int8 value distribution"},
         "us_per_call": ms_per_step * 1e3, "decode_tok_per_s": batch * world / (ms_per_step * 1e-3),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_source": peak_src, "frac_of_nominal_8TBs": achieved / 8000.0, "kernel": "decode_kernel<128,false>",
@@ -295,11 +409,22 @@ def run_ours(args, rank, world, local_rank):
         "gpu_launches": args.steps * 3,
         "clocks": clocks,
     }
+    if check is not None:
+        line["output_check"] = check
+    if strong is not None:
+        s_ms = strong / args.steps
+        line["strong"] = {
+            "workload": f"the fixed {BATCH} x {CTX} layer, {BATCH // world} requests per GPU",
+            "us_per_step": s_ms * 1e3, "value": BATCH * CTX * HKV * D * 2 / (s_ms * 1e-3) / 1e9, "unit": UNIT,
+            "decode_tok_per_s": BATCH / (s_ms * 1e-3),
+            "collective": ("none (one GPU)" if world == 1 else
+                           f"NCCL all_gather of [{BATCH // world}, {HQ}, {D}] bf16 output rows per rank inside the timed step"),
+            "speedup_vs_one_gpu_step_of_this_run": ms_per_step / s_ms,
+            "note": "the weak-scaling step above runs the whole 128-request layer on every GPU, so its time is this "
+                    "run's one-GPU time for the fixed layer"}
     if world == 1 and not args.no_cpu:
         line["cpu_baseline"] = cpu_baseline()
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 # --------------------------------------------------------------------------------------------------------
@@ -491,11 +616,11 @@ def run_prefill_suite(args):
 # --------------------------------------------------------------------------------------------------------
 # --workload model_step: full decode step of a Qwen2.5-7B-geometry decoder (a caller of the hot path)
 # --------------------------------------------------------------------------------------------------------
-def run_model_step(args, rank, world, local_rank):
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+def model_step_record(args, rank, world, dev, steps):
+    """Benchmark configuration 4: one decode step of a 28-layer Qwen2.5-7B-geometry decoder (random bf16 weights,
+    kvq_b200/decode_step.py), `--model-requests` (512) requests x `--model-ctx` (6144) context in the int8_static
+    paged cache, requests sharded over the GPUs, weights replicated, no collective inside the step. Every rank
+    times `steps` graph replays; the record carries the slowest rank's time."""
     from kvq_b200.decode_step import DecodeStep
 
     total_requests, ctx = args.model_requests, args.model_ctx
@@ -507,12 +632,12 @@ def run_model_step(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(3):
         model.step()
     sync_all()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         model.step()
     b.record()
     sync_all()
@@ -521,18 +646,98 @@ def run_model_step(args, rank, world, local_rank):
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
-    if rank == 0:
-        tpot = ms / args.steps
-        print(json.dumps({
-            "workload": "model_step", "metric": "decode_tokens_per_s", "value": batch * world / (tpot * 1e-3), "unit": "tok/s",
-            "tpot_ms": tpot, "n_gpus": world, "steps": args.steps, "scaling": "strong (fixed 512 requests)" if world > 1 else "n/a",
+    kv_b, w_b = model.kv_bytes_per_step(), model.weight_bytes()
+    del model
+    torch.cuda.empty_cache()
+    if rank != 0:
+        return None
+    tpot = ms / steps
+    peak, _ = peaks()
+    return {"workload": "model_step", "metric": "decode_tokens_per_s", "value": batch * world / (tpot * 1e-3), "unit": "tok/s",
+            "tpot_ms": tpot, "n_gpus": world, "steps": steps, "scaling": "strong (fixed total requests)",
             "config": {"model": "Qwen2.5-7B geometry, random-init bf16 weights, vocab 152064", "requests": batch * world,
                        "requests_per_gpu": batch, "context": ctx, "kv_cache": "int8_static paged, block 16",
-                       "parallelism": f"requests sharded over {world} GPU(s), weights replicated"},
-            "kv_bytes_per_step_per_gpu": model.kv_bytes_per_step(), "weight_bytes_per_gpu": model.weight_bytes(),
-            "data": "synthetic"}), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+                       "parallelism": f"requests sharded over {world} GPU(s), weights replicated, CUDA-graphed step"},
+            "kv_bytes_per_step_per_gpu": kv_b, "weight_bytes_per_gpu": w_b,
+            "hbm_floor_ms": (kv_b + w_b) / (peak * 1e9) * 1e3,
+            "frac_of_hbm_floor": (kv_b + w_b) / (peak * 1e9) * 1e3 / tpot, "data": "synthetic"}
+
+
+# --------------------------------------------------------------------------------------------------------
+# --suite ref_kernel: the reference's own CUDA kernels, built for this GPU from a checkout given at run time
+# --------------------------------------------------------------------------------------------------------
+def run_ref_kernel_suite(args):
+    """Side-by-side device times of this library and of the reference's CUDA extension (kvq/cuda/int8_kv.cu, JIT-built
+    by the reference's own kvq/cuda_kernels.py:ext() from the checkout at --ref-path; nothing of it is part of this
+    repository) on the same inputs: eager calls, a 256 MB L2 flush before each, median of 10. One JSON line per case,
+    with the difference between the two kernels' outputs."""
+    import statistics
+
+    if not args.ref_path or not os.path.exists(os.path.join(args.ref_path, "kvq", "cuda", "int8_kv.cu")):
+        print(json.dumps({"suite": "ref_kernel", "unavailable": "--ref-path must point at a checkout of the reference "
+                          "(kvq/cuda/int8_kv.cu)"}), flush=True)
+        return
+    sys.path.insert(0, os.path.abspath(args.ref_path))
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    from kvq import cuda_kernels as rck   # the reference's module
+
+    from kvq_b200 import cuda_kernels as ck
+    from kvq_b200 import workloads
+
+    t0 = time.time()
+    rck.ext()
+    build_s = round(time.time() - t0, 1)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(reps):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(ts)
+
+    common = {"suite": "ref_kernel", "timing": "eager call, 256 MB L2 flush before each, CUDA events, median of 10",
+              "reference_build_s": build_s}
+    cases = ((128, 32768, 1, None, "headline 128 x 32768"), (16, 32768, 1, None, "16 x 32768 (one rank of 8)"),
+             (1, 32768, 1, None, "1 x 32768"), (128, 4096, 1, None, "128 x 4096"),
+             (256, 0, 8, (1024, 8192), "config 3: 256 requests, q_len 8, ctx U[1024, 8192]"))
+    for batch, ctx, q_len, rng, name in cases:
+        c = workloads.decode_batch_on_device(batch, ctx, dev, seed=1002 if q_len == 1 else 1003, q_len=q_len, ctx_range=rng)
+        st = c["static"]
+        out_r, out_o = torch.zeros_like(c["q"]), torch.zeros_like(c["q"])
+        T = c["q"].shape[0]
+        segm = None
+        if batch <= 32:   # vLLM hands split-KV scratch to small batches (16 segments)
+            segm = (torch.empty(T, HQ, 16, D, device=dev), torch.empty(T, HQ, 16, device=dev), torch.empty(T, HQ, 16, device=dev))
+        meta = (c["cu_seqlens_q"], c["seq_lens"], c["block_table"], c["softmax_scale"], st)
+        t_ref = timed(lambda: rck.decode_attention(c["q"], c["kq"], c["vq"], out_r, *meta, segm=segm, max_query_len=q_len))
+        t_our = timed(lambda: ck.decode_attention(c["q"], c["kq"], c["vq"], out_o, *meta, max_query_len=q_len))
+        nbytes = kv_bytes(c["seq_lens_list"])
+        d = (out_r.float() - out_o.float()).abs()
+        print(json.dumps(dict(common, case=name, reference_us=round(t_ref, 1), ours_us=round(t_our, 1),
+                              reference_GBps=round(nbytes / t_ref / 1e3), ours_GBps=round(nbytes / t_our / 1e3),
+                              speedup=round(t_ref / t_our, 2), max_abs_diff_between_kernels=float(d.max()),
+                              identical_fraction=float((d == 0).float().mean()))), flush=True)
+        del c, out_r, out_o
+    for T in (128, 8192):
+        w = workloads.write_case(1001, T, HKV, D, num_blocks=4096, smooth=False)
+        st = {k: v.to(dev) for k, v in w["static"].items()}
+        key, value, slots = w["key"].to(dev), w["value"].to(dev), w["slots"].to(dev)
+        kc = torch.zeros(4096, BLOCK, HKV, D, dtype=torch.int8, device=dev)
+        vc, kc2, vc2 = torch.zeros_like(kc), torch.zeros_like(kc), torch.zeros_like(kc)
+        t_ref = timed(lambda: rck.quant_reshape_and_cache(key, value, kc, vc, slots, st))
+        t_our = timed(lambda: ck.quant_reshape_and_cache(key, value, kc2, vc2, slots, st))
+        print(json.dumps(dict(common, case=f"quantize + cache write, {T} tokens", reference_us=round(t_ref, 1),
+                              ours_us=round(t_our, 1), speedup=round(t_ref / t_our, 2),
+                              cache_bytes_equal=bool(torch.equal(kc, kc2) and torch.equal(vc, vc2)))), flush=True)
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch, from the ncu capture summarised in
@@ -548,14 +753,18 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the oracle check of the timed batch's outputs")
+    ap.add_argument("--no-model-step", action="store_true", help="skip the model_step sub-record (configuration 4)")
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU (default: the headline 128)")
     ap.add_argument("--ctx", type=int, default=CTX, help="context length (default: the headline 32768)")
     ap.add_argument("--workload", default="attention", choices=["attention", "model_step"],
-                    help="model_step: full 28-layer decode step (512 requests x 6144 context over all GPUs)")
+                    help="model_step: only the full 28-layer decode step (512 requests x 6144 context over all GPUs)")
     ap.add_argument("--model-requests", type=int, default=512)
     ap.add_argument("--model-ctx", type=int, default=6144)
-    ap.add_argument("--suite", default=None, choices=["kernels", "prefill"],
-                    help="extra per-kernel lines instead of the headline (prefill: long-query attention, both routes)")
+    ap.add_argument("--suite", default=None, choices=["kernels", "prefill", "ref_kernel"],
+                    help="extra per-kernel lines instead of the headline (prefill: long-query attention, both routes; "
+                         "ref_kernel: the reference's CUDA extension built from --ref-path, side by side)")
+    ap.add_argument("--ref-path", default=None, help="checkout of the reference (for --suite ref_kernel)")
     ap.add_argument("--q-len", type=int, default=1, help="query tokens per request (profile runs; headline is 1)")
     ap.add_argument("--ctx-min", type=int, default=0, help="draw contexts uniformly from [ctx-min, ctx] (profile runs)")
     ap.add_argument("--profile", action="store_true", help="kernel timings only, exact --warmup (for ncu captures)")
@@ -564,22 +773,37 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))
     if args.impl == "reference":
-        if args.steps == 20 and args.warmup == 5:
-            args.steps, args.warmup = 5, 3
         run_reference_arm(args, rank)
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU (there is no CPU path for the product arm)")
-    if args.workload == "model_step":
-        run_model_step(args, rank, world, local_rank)
-        return
     if args.suite == "kernels":
         run_suite(args)
         return
     if args.suite == "prefill":
         run_prefill_suite(args)
         return
-    run_ours(args, rank, world, local_rank)
+    if args.suite == "ref_kernel":
+        run_ref_kernel_suite(args)
+        return
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if args.workload == "model_step":
+        line = model_step_record(args, rank, world, dev, args.steps)
+    else:
+        line = run_ours(args, rank, world, local_rank)
+        headline = (args.batch, args.ctx, args.q_len) == (BATCH, CTX, 1) and not args.profile
+        if headline and not args.no_model_step and args.model_requests % world == 0:
+            torch.cuda.empty_cache()
+            ms = model_step_record(args, rank, world, dev, min(args.steps, 10))
+            if line is not None:
+                line["model_step"] = ms
+    if rank == 0 and line is not None:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

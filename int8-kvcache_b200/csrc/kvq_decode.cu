@@ -82,13 +82,6 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-#ifdef KVQ_TIMELINE   // debug builds only: per-CTA cycle stamps of the first item, read back by a probe
-__device__ long long g_timeline[1024 * 16];
-#define KVQ_TL(i) do { if (threadIdx.x == 0 && first_seg) g_timeline[blockIdx.x * 16 + (i)] = clock64(); } while (0)
-#else
-#define KVQ_TL(i) do { } while (0)
-#endif
-
 // Unevaluated sum hi + lo of two floats (|lo| <= ulp(hi) / 2): ~48 bits of significand without FP64 instructions.
 struct ff {
   float hi, lo;
@@ -508,14 +501,12 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   bool ok = true;
   int u = ubeg;
   bool first_seg = true;
-  KVQ_TL(0);
   while (u < uend) {
     // ---- find the request that owns unit u: prefix[r] <= u < prefix[r + 1] ----
     for (int r = tid; r < a.num_seqs; r += NTHREADS)
       if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
     __syncthreads();
     const int req = s_req;
-    KVQ_TL(1);
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
     const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, a.hg);
     const int nchunks = rs.nchunks;
@@ -620,7 +611,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       // HBM busy through the q prologue; a shared ring keeps one stage back for the other warps of the group.
       if (ok)
         for (int ip = 0; ip < npw && msl + GS * ip < (GS == 1 ? NSTAGE : PD); ++ip) issue(ip, msl + GS * ip);
-      KVQ_TL(2);
 
       // -- q prologue for every m tile of the group --
       if (early_q) {
@@ -661,7 +651,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
           for (int e = 0; e < (ROWS16 ? 4 : 2); ++e) ts.acc[j][e] = 0.f;
       }
       const int lim_all = L - qlen + 1;  // every row sees keys below this
-      KVQ_TL(3);
 
       // -- main loop over the group's chunks --
       for (int i = 0; i < nig && ok; ++i) {
@@ -672,7 +661,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         const int st = cst;
         ok = ok && __all_sync(0xffffffffu, mbar_wait(gfull + st * 8, cpass & 1));
         if (!ok) break;
-        if (i == 0) KVQ_TL(4);
         if (active) {
           const uint32_t sk = gring + st * SB;
           chunk_step<D, ROWS16>(ts, sk, sk + SB / 2, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t, HS,
@@ -682,7 +670,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         if (GS > 1 && lane == 0) mbar_arrive(gempty + st * 8);
         if (++cst == RD) cst = 0, ++cpass;
       }
-      KVQ_TL(5);
       if (!ok) atomicExch(a.hdr, 1);
 
       // -- combine the warps that worked on the same m tile (slot msl of every group): weights exp(m_w - M) --
@@ -713,7 +700,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         }
       }
       __syncthreads();
-      KVQ_TL(6);
 
       // -- epilogue: 4 channels per thread and step; s_v applied here --
       const int slot_base = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * a.part_rows;
@@ -753,7 +739,6 @@ __global__ void __launch_bounds__(NTHREADS, 2)
       // generic-proxy writes to the ring (s_acc) come before the next item's TMA writes
       fence_proxy_async();
       __syncthreads();
-      KVQ_TL(7);
       u += c1 - c0;
       first_seg = false;
       if (u == uend && tid == 0) {
@@ -1251,9 +1236,3 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_
                                    ws, KVQ_STATIC_WS_BYTES, stream);
 }
 
-#ifdef KVQ_TIMELINE
-extern "C" __attribute__((visibility("default"))) int kvq_debug_timeline(long long* host, int n) {
-  KVQ_CUDA(cudaMemcpyFromSymbol(host, g_timeline, sizeof(long long) * n));
-  return KVQ_OK;
-}
-#endif

@@ -149,15 +149,6 @@ __global__ void __launch_bounds__(256) prefill_plan_kernel(const int32_t* __rest
 constexpr int WS_BN = 128;           // keys per step
 constexpr int WS_THREADS = 14 * 32;
 constexpr int WS_TMEM_COLS = 512;
-#ifdef KVQ_PF_TIMELINE
-__device__ long long g_pf_timeline[3 * 64 * 8];   // [role][step][event]
-#define PF_TL(role, step, ev)                                                                      \
-  do {                                                                                             \
-    if (blockIdx.x == gridDim.x / 2 && (step) < 64) g_pf_timeline[((role) * 64 + (step)) * 8 + (ev)] = clock64(); \
-  } while (0)
-#else
-#define PF_TL(role, step, ev) do { } while (0)
-#endif
 enum WsBar {
   WB_STGK = 0,        // int8 K boxes of a step landed (TMA)
   WB_STGV = 1,
@@ -346,10 +337,8 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     float m_ref = -1e30f, l_sum = 0.f;
     bool ok = true;
     for (int j = 0; j < nkt && ok; ++j) {
-      if (tid == 0) PF_TL(0, j, 0);
       ok = ws_wait(bar(WB_S_READY + t), j & 1, abort_flag);
       if (!ok) break;
-      if (tid == 0) PF_TL(0, j, 1);
       tc_fence_after();
       // pass 1: row maximum of the step's 128 scores (64 columns per round trip to tensor memory)
       const int n_base = j * WS_BN;
@@ -379,7 +368,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         }
         mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       }
-      if (tid == 0) PF_TL(0, j, 2);
       const float tile_max = mx * c_row;   // c_row > 0
       const bool grow = tile_max > m_ref + 8.f;
       float alpha = 1.f;
@@ -400,7 +388,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
           tmem_st32(t_o + c, o);
         }
       }
-      if (tid == 0) PF_TL(0, j, 3);
       // pass 2: P = exp2(S * c_row - m_ref) as fp16 pairs, written over the first half of S chunk by chunk
       // (chunk i reads S columns [32 i, 32 i + 32) and then writes P columns [16 i, 16 i + 16): never ahead of a
       // read). P.V may start on the first 64 keys while the last 64 are still being computed.
@@ -448,7 +435,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         }
         l_sum += ls;
       }
-      if (tid == 0) PF_TL(0, j, 4);
     }
     // ---- epilogue: O / denominator * s_v -> bf16 ----
     if (ok && nkt > 0) ok = ws_wait(bar(WB_O_DONE + t), (nkt - 1) & 1, abort_flag);
@@ -492,27 +478,20 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     bool ok = true;
     for (int j = 0; j < nk && ok; ++j) {
       const int s = j & 1;
-      if (ctid == 0) PF_TL(1, j, 0);
       ok = ws_wait(bar(WB_STGK), j & 1, abort_flag);
-      if (ctid == 0) PF_TL(1, j, 1);
       if (ok && j >= 2) ok = ws_wait(bar(WB_KF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
-      if (ctid == 0) PF_TL(1, j, 2);
       widen_step<D>(p_base + Gm::OFF_SK, p_base + Gm::OFF_K + s * Gm::KV_TILE, ctid);
       fence_proxy_async();
       mbar_arrive(bar(WB_KF_READY + s));
       mbar_arrive(bar(WB_STGK_FREE));   // the landing zone may be refilled (producer warp)
-      if (ctid == 0) PF_TL(1, j, 3);
       ok = ws_wait(bar(WB_STGV), j & 1, abort_flag);
-      if (ctid == 0) PF_TL(1, j, 5);
       if (ok && j >= 2) ok = ws_wait(bar(WB_VF_FREE + s), ((j - 2) >> 1) & 1, abort_flag);
       if (!ok) break;
-      if (ctid == 0) PF_TL(1, j, 6);
       widen_step<D>(p_base + Gm::OFF_SV, p_base + Gm::OFF_V + s * Gm::KV_TILE, ctid);
       fence_proxy_async();
       mbar_arrive(bar(WB_VF_READY + s));
       mbar_arrive(bar(WB_STGV_FREE));
-      if (ctid == 0) PF_TL(1, j, 7);
     }
   } else if (warp == 13) {
     // ================= TMA producer: lane i < 8 loads the i-th 16-key box of a step =================
@@ -577,9 +556,7 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
     if (ok && nk > 0) umma_commit(bar(WB_KF_FREE));
     for (int j = 0; j < nk && ok; ++j) {
       const int s = j & 1;
-      PF_TL(2, j, 0);
       ok = ws_wait_thread(bar(WB_VF_READY + s), (j >> 1) & 1, abort_flag);
-      PF_TL(2, j, 1);
       const uint64_t d_vs = d_v + static_cast<uint64_t>((s * Gm::KV_TILE) >> 4);
 #pragma unroll
       for (int t = 0; t < 2; ++t) {
@@ -590,7 +567,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
           ok = ok && ws_wait_thread(bar(WB_P_READY + t * 2 + h), j & 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          if (h == 0) PF_TL(2, j, 2 + 2 * t);
 #pragma unroll
           for (int ks = 4 * h; ks < 4 * h + 4; ++ks)   // 16 keys = 8 columns of packed P per k step
             umma_f16_ts(tmem + 2 * WS_BN + t * D, tmem + t * WS_BN + ks * 8,
@@ -599,7 +575,6 @@ __global__ void __launch_bounds__(WS_THREADS, 1)
         if (!ok) continue;
         umma_commit(bar(WB_O_DONE + t));
         if (j + 1 < nkt) issue_qk(t, j + 1);   // executes after the P.V above: S[t] (and the P inside it) is free again
-        PF_TL(2, j, 3 + 2 * t);
       }
       if (ok) {
         umma_commit(bar(WB_VF_FREE + s));
@@ -722,8 +697,3 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_prefill_attention
   return KVQ_OK;
 }
 
-#ifdef KVQ_PF_TIMELINE
-extern "C" __attribute__((visibility("default"))) int kvq_debug_pf_timeline(long long* host, int n) {
-  return cudaMemcpyFromSymbol(host, g_pf_timeline, sizeof(long long) * n) == cudaSuccess ? 0 : 1;
-}
-#endif

@@ -11,6 +11,7 @@ All tensors must live on the current CUDA device; work is enqueued on torch's cu
 synchronizes, and every call can be captured in a CUDA graph.
 """
 import os
+import warnings
 from dataclasses import dataclass
 
 import numpy as np
@@ -18,10 +19,25 @@ import torch
 
 from . import _native
 
-# q_len at or below this: INT8 kernel; above: dequantize + FlashAttention (kvq/cuda_kernels.py:19-21).
-# The INT8 kernel itself handles at most 8 query tokens per request.
-SHORT_Q = int(os.environ.get("KVQ_SHORT_Q", 8))
+# q_len at or below SHORT_Q: INT8 kernel; above: the long-query path (kvq/cuda_kernels.py:19-21).
+# The INT8 kernel handles at most KERNEL_QMAX query tokens per request, so KVQ_SHORT_Q can only lower the
+# threshold: a larger value is clamped (with a warning) and requests with 9 or more query tokens always take the
+# long path. Every routing decision (decode_attention, plan_long, long_attention, prefill_attention, the backend's
+# CUDA-graph support level) uses this one effective value.
 KERNEL_QMAX = 8
+
+
+def _short_q_from_env():
+    asked = int(os.environ.get("KVQ_SHORT_Q", KERNEL_QMAX))
+    if asked < 1:
+        raise RuntimeError(f"kvq_b200: KVQ_SHORT_Q must be at least 1, got {asked}")
+    if asked > KERNEL_QMAX:
+        warnings.warn(f"kvq_b200: KVQ_SHORT_Q={asked} exceeds the INT8 kernel's limit of {KERNEL_QMAX} query tokens per "
+                      f"request; using {KERNEL_QMAX} (longer queries take the long-query path)", stacklevel=2)
+    return min(asked, KERNEL_QMAX)
+
+
+SHORT_Q = _short_q_from_env()
 
 
 def ext():
@@ -94,24 +110,45 @@ def quant_q(q, k_scale, group=None):
     return q_i8, q_s
 
 
-_WORKSPACES = {}
+class _StreamWorkspaces:
+    """Scratch buffers of one kernel family, one per (device, stream): calls on different streams of a device can
+    overlap on the GPU, so they must not share scratch; calls on one stream are ordered by it.
+
+    A buffer that has been handed out is never freed or replaced in place: a CUDA graph that captured a call
+    replays with the buffer's raw address, whatever Python does afterwards. When a larger batch needs more, a new
+    buffer is allocated and the old one is kept alive in `retired`. A buffer first needed while its stream is
+    capturing is allocated inside the capture, i.e. from the graph's memory pool, and stays referenced here."""
+
+    def __init__(self, size_fn, floor_args):
+        self.size_fn, self.floor_args = size_fn, floor_args
+        self.live, self.retired = {}, []
+
+    def get(self, device, need):
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        key = (index, torch.cuda.current_stream(device).cuda_stream)
+        ws = self.live.get(key)
+        if ws is None or ws.numel() < need:
+            if ws is not None:
+                self.retired.append(ws)
+            ws = torch.empty(max(need, self.size_fn(*self.floor_args)), dtype=torch.uint8, device=device)
+            self.live[key] = ws
+        return ws
+
+    def peek(self, device):
+        index = device.index if device.index is not None else torch.cuda.current_device()
+        return self.live.get((index, torch.cuda.current_stream(device).cuda_stream))
+
+
+# sized for a generous batch (4096 requests, ~39 MB) so that it rarely grows
+_WORKSPACES = _StreamWorkspaces(lambda n, d: ext().kvq_decode_workspace_size(n, d), (4096, 128))
 
 
 def decode_workspace(device, num_seqs, head_dim):
-    """Per-device scratch of the attention kernels (split-KV partials and the work plan). Grown on demand and
-    shared by every call on the device: calls are ordered by the stream they run on."""
+    """Scratch of the attention kernels (work plan and split-KV partials) for torch's current stream on `device`."""
     need = ext().kvq_decode_workspace_size(num_seqs, head_dim)
     if need == 0:
         raise RuntimeError("kvq_b200: " + ext().kvq_last_error().decode())
-    key = (device.index if device.index is not None else torch.cuda.current_device())
-    ws = _WORKSPACES.get(key)
-    if ws is None or ws.numel() < need:
-        # sized for a generous batch so that it rarely grows (growing while a CUDA graph that captured the old
-        # buffer is alive is fine: the graph keeps the old tensor's memory through its own pool)
-        ws = torch.empty(max(need, ext().kvq_decode_workspace_size(max(num_seqs, 4096), 128)), dtype=torch.uint8,
-                         device=device)
-        _WORKSPACES[key] = ws
-    return ws
+    return _WORKSPACES.get(device, need)
 
 
 def decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static,
@@ -145,16 +182,16 @@ def decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_tab
         q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
         ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(1), k_cache.size(2), q.size(2),
         k_cache.size(1), k_cache.size(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1), kc_sb, kc_sn, kc_sh,
-        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, int(max_query_len), min(SHORT_Q, KERNEL_QMAX),
-        ws.data_ptr(), ws.numel(), _stream()))
+        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, int(max_query_len), SHORT_Q, ws.data_ptr(), ws.numel(),
+        _stream()))
     return out
 
 
 def decode_status(device=None):
-    """Debug: status word of the last attention call on `device` (0 = clean). Synchronizes the stream."""
+    """Debug: status word of the last attention call on `device` and torch's current stream (0 = clean).
+    Synchronizes the stream."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _WORKSPACES.get(key)
+    ws = _WORKSPACES.peek(device)
     if ws is None:
         return 0
     import ctypes
@@ -261,7 +298,7 @@ def long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table
     return out
 
 
-_PREFILL_WS = {}
+_PREFILL_WS = _StreamWorkspaces(lambda n: ext().kvq_prefill_workspace_size(n), (4096,))
 
 
 def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static):
@@ -288,12 +325,7 @@ def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_ta
     kc, kc_sb, kc_sn, kc_sh = _cache_args(k_cache)
     vc, vc_sb, vc_sn, vc_sh = _cache_args(v_cache)
     pk, pv = _scale_flags(ks, vs)
-    key = q.device.index if q.device.index is not None else torch.cuda.current_device()
-    need = ext().kvq_prefill_workspace_size(num_seqs)
-    ws = _PREFILL_WS.get(key)
-    if ws is None or ws.numel() < need:
-        ws = torch.empty(max(need, ext().kvq_prefill_workspace_size(4096)), dtype=torch.uint8, device=q.device)
-        _PREFILL_WS[key] = ws
+    ws = _PREFILL_WS.get(q.device, ext().kvq_prefill_workspace_size(num_seqs))
     _native.check(ext().kvq_int8_prefill_attention(
         q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
         ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(0), q.size(1), k_cache.size(2), q.size(2),
@@ -305,11 +337,10 @@ def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_ta
 def prefill_status(device=None):
     """Debug: status word of the last prefill_attention call on `device` (0 = clean). Synchronizes the stream."""
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else device
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    ws = _PREFILL_WS.get(key)
+    ws = _PREFILL_WS.peek(device)
     if ws is None:
         return 0
-    torch.cuda.current_stream().synchronize()
+    torch.cuda.current_stream(device).synchronize()
     return int(ws[:4].view(torch.int32).item())
 
 

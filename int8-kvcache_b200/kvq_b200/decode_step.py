@@ -58,6 +58,7 @@ class DecodeStep:
         self.next_tokens = torch.zeros_like(self.tokens)
         self.attn_out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=device)
         self.graph = None
+        self.trace = None   # set to a list before an eager forward() to keep every layer's (q, k, v, attn_out)
 
     def kv_bytes_per_step(self):
         g = self.g
@@ -87,6 +88,8 @@ class DecodeStep:
             kc, vc = self.kv[i, 0], self.kv[i, 1]
             ck.quant_reshape_and_cache(k, v, kc, vc, self.slots, l["static"])
             ck.decode_attention(q, kc, vc, self.attn_out, self.cu, self.seq_lens, self.block_table, scale, l["static"])
+            if self.trace is not None:
+                self.trace.append(dict(q=q.clone(), k=k.clone(), v=v.clone(), attn_out=self.attn_out.clone()))
             x = x + self.attn_out.view(self.batch, hq * d) @ l["wo"]
             gu = self._rms(x, l["ln2"]) @ l["wgu"]
             x = x + (torch.nn.functional.silu(gu[:, :g["mlp"]]) * gu[:, g["mlp"]:]) @ l["wdown"]

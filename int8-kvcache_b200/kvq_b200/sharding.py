@@ -35,13 +35,27 @@ def shard_batch(cu_seqlens_q, seq_lens, block_table, owned):
     return new_cu, seq_lens[idx], block_table[idx], torch.tensor(rows, dtype=torch.long)
 
 
-def gather_outputs(local_out, rows_per_rank, group=None):
+def gather_outputs(local_out, rows_per_rank, group=None, out=None):
     """All-gather of per-rank output rows [T_r, Hq, D] into rank order [sum T_r, Hq, D]. rows_per_rank lists T_r for
-    every rank (known to all ranks from the sharding rule), so ragged shards are padded to the largest."""
+    every rank (known to all ranks from the sharding rule). Equal shards go through one all_gather_into_tensor
+    straight into `out` (allocated here when not given: pass a persistent buffer to keep the step allocation-free);
+    ragged shards are padded to the largest and trimmed after the gather."""
     world = dist.get_world_size(group)
+    if len(rows_per_rank) != world or local_out.shape[0] != rows_per_rank[dist.get_rank(group)]:
+        raise ValueError(f"rows_per_rank {rows_per_rank} does not describe this group (world {world}, local rows "
+                         f"{local_out.shape[0]})")
+    total = sum(rows_per_rank)
+    if out is None:
+        out = local_out.new_empty((total,) + tuple(local_out.shape[1:]))
+    elif out.shape[0] != total or out.shape[1:] != local_out.shape[1:] or not out.is_contiguous():
+        raise ValueError("out must be a contiguous [sum(rows_per_rank), ...] tensor")
+    if len(set(rows_per_rank)) == 1 and local_out.is_contiguous():
+        dist.all_gather_into_tensor(out, local_out, group=group)
+        return out
     t_max = max(rows_per_rank)
     padded = local_out.new_zeros((t_max,) + tuple(local_out.shape[1:]))
     padded[:local_out.shape[0]] = local_out
     parts = [torch.empty_like(padded) for _ in range(world)]
     dist.all_gather(parts, padded, group=group)
-    return torch.cat([p[:n] for p, n in zip(parts, rows_per_rank)], dim=0)
+    torch.cat([p[:n] for p, n in zip(parts, rows_per_rank)], dim=0, out=out)
+    return out

@@ -94,6 +94,21 @@ def write_case(seed, tokens, hkv, d, num_blocks, block_size=16, per_channel=True
             "block_size": block_size}
 
 
+def serving_lengths(seed=0, chunks=68, decodes=188):
+    """(q_lens, seq_lens) of one chunked-prefill serving step: `chunks` prompt chunks of 39..73 query tokens whose
+    context is the chunk plus 0..19 earlier tokens, among `decodes` single-token requests with contexts of
+    100..399, in a seeded random order. Short requests between long ones are the batch shape on which a
+    FlashAttention call over the whole batch must not see requests with zero keys."""
+    gen = torch.Generator(device="cpu").manual_seed(seed)
+    q_chunks = torch.randint(39, 74, (chunks,), generator=gen)
+    ctx_chunks = q_chunks + torch.randint(0, 20, (chunks,), generator=gen)
+    ctx_dec = torch.randint(100, 400, (decodes,), generator=gen)
+    q = torch.cat([q_chunks, torch.ones(decodes, dtype=torch.int64)])
+    ctx = torch.cat([ctx_chunks, ctx_dec])
+    order = torch.randperm(chunks + decodes, generator=gen)
+    return q[order].tolist(), ctx[order].tolist()
+
+
 # Benchmark configurations (geometry of one Qwen2.5-7B attention layer).
 HQ, HKV, D, BLOCK = 28, 4, 128, 16
 

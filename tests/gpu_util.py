@@ -8,6 +8,37 @@ from oracle import kvq_oracle as orc
 
 DEV = "cuda"
 
+MAX_ABS, MEAN_ABS, REL_L2 = 1e-2, 1e-3, 5e-3
+
+
+def bf16_ulp(x):
+    """Spacing of bf16 numbers at |x| (8 significand bits): 2^(floor(log2 |x|) - 7)."""
+    ax = np.maximum(np.abs(np.asarray(x, np.float64)), 2.0 ** -126)
+    return 2.0 ** (np.floor(np.log2(ax)) - 7)
+
+
+def assert_close(ref, out, what=""):
+    """The attention bar. ref: fp32 result of the oracle / the reference; out: the kernel's bf16 output as fp32.
+
+    Where |ref| < 2: max-abs 1e-2 and mean-abs 1e-3 against the fp32 reference outright. Where |ref| >= 2 a
+    correctly rounded bf16 store alone can be off by up to half an ulp = 2^-7 .. 2^-5, so there the kernel must
+    hit the bf16 rounding of the reference or one of its two neighbours: |out - bf16(ref)| <= 1 bf16 ulp.
+    Plus the reference's own bound for its CUDA kernel, rel_l2 < 5e-3, over everything."""
+    ref, out = np.asarray(ref, np.float32), np.asarray(out, np.float32)
+    err = orc.compare(ref, out)
+    d = np.abs(ref.astype(np.float64) - out.astype(np.float64))
+    small = np.abs(ref) < 2.0
+    if small.any():
+        err["max_abs_small"], err["mean_abs_small"] = float(d[small].max()), float(d[small].mean())
+        assert err["max_abs_small"] <= MAX_ABS and err["mean_abs_small"] < MEAN_ABS, (what, err)
+    if (~small).any():
+        big = ~small
+        steps = np.abs(orc.round_to_bf16(ref[big]).astype(np.float64) - out[big]) / bf16_ulp(ref[big])
+        err["max_ulp_large"] = float(steps.max())
+        assert err["max_ulp_large"] <= 1.0, (what, err)
+    assert err["rel_l2"] < REL_L2, (what, err)
+    return err
+
 
 def to_dev(static):
     return {k: v.to(DEV) for k, v in static.items()}

@@ -183,3 +183,32 @@ def test_prefill_argument_errors_are_reported_without_a_gpu():
     assert lib.kvq_int8_prefill_attention(*args) == 1 and b"group" in lib.kvq_last_error()
     args[10] = 0                                    # empty batch: silent success, like the reference's early returns
     assert lib.kvq_int8_prefill_attention(*args) == 0
+
+
+def test_short_q_is_one_threshold_everywhere():
+    """KVQ_SHORT_Q above the INT8 kernel's limit is clamped with a warning, and every routing decision uses the
+    clamped value: a request with 9 query tokens is planned as long (never left to a kernel that would skip it),
+    one with 8 as short. A lower value is honoured; zero or less is rejected."""
+    import subprocess
+    import sys
+
+    code = (
+        "import sys, warnings; sys.path.insert(0, %r)\n"
+        "with warnings.catch_warnings(record=True) as w:\n"
+        "    warnings.simplefilter('always')\n"
+        "    from kvq_b200 import cuda_kernels as ck\n"
+        "import numpy as np\n"
+        "plan = ck.plan_long(np.array([0, 9, 17, 18]), np.array([40, 50, 60]), 16)\n"
+        "print(ck.SHORT_Q, ck.KERNEL_QMAX, len(w), None if plan is None else plan.src_req.tolist())\n"
+    ) % os.path.join(ROOT, "int8-kvcache_b200")
+
+    def run(value):
+        env = dict(os.environ, KVQ_SHORT_Q=value)
+        return subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True)
+
+    res = run("1000000")
+    assert res.returncode == 0, res.stderr
+    assert res.stdout.split(None, 3) == ["8", "8", "1", "[0, 0, 0]\n"], res.stdout   # 9 tokens -> 3 pages copied, 8 -> none
+    res = run("4")
+    assert res.stdout.split(None, 3) == ["4", "8", "0", "[0, 0, 0, 1, 1, 1, 1]\n"], res.stdout
+    assert run("0").returncode != 0

@@ -122,3 +122,35 @@ def test_calibration_statistics_match_reference_hook():
         for f, v in res.items():
             want = fx[f"scales_{gran}_{method}_{int(smooth)}_{f}"]
             assert np.allclose(v.numpy(), want, rtol=1e-6, atol=0), (gran, method, smooth, f)
+
+
+def test_numpy_oracle_agrees_with_the_staged_reference_modules():
+    """Where oracle/_ref holds the reference's own modules (byte-compiled by oracle/build_ref.py from a checkout), the
+    numpy restatement is compared with them directly on fresh seeded cases, beyond the committed fixtures: decode,
+    short multi-token queries and a long request (implementation A), per-channel and per-head scales."""
+    import torch
+    from oracle import build_ref
+    from kvq_b200 import workloads
+
+    mods = build_ref.load()
+    if mods is None:
+        pytest.skip("oracle/_ref not built (no reference checkout on this machine)")
+    quant, ref_attn, int8_ref = mods
+    for seed, per_channel in ((201, True), (202, False)):
+        case = workloads.paged_case(seed, 12, 2, 128, [1, 5, 8, 1, 20], [300, 77, 1030, 16, 150], per_channel=per_channel,
+                                    smooth=True, q_std=3.0)
+        st = case["static"]
+        gran = "per_channel" if per_channel else "per_head"
+        fn = int8_ref.paged_static_attention(int8_ref.Cfg(smooth_k=True, p_tile=32, k_gran=gran, v_gran=gran), st,
+                                             cache_is_int8=True, short_q=8)
+        want = fn(case["q"].float(), case["kq"], case["vq"], case["cu_seqlens_q"], case["seq_lens"], case["block_table"],
+                  case["softmax_scale"]).numpy()
+        got = orc.paged_static_attention(case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(),
+                                         case["cu_seqlens_q"].numpy(), case["seq_lens"].numpy(), case["block_table"].numpy(),
+                                         case["softmax_scale"], st["k_scale"].numpy(), st["v_scale"].numpy())
+        d = np.abs(want - got)
+        assert d.max() < ATTN_TOL["max_abs"] and d.mean() < ATTN_TOL["mean_abs"]
+        # cache bytes through the reference's quantize
+        kq = quant.quantize(case["k"].float() - st["k_mu"], st["k_scale"]).numpy()
+        assert np.array_equal(kq, case["kq"].numpy())
+        assert np.array_equal(orc.quantize(case["k"].float().numpy() - st["k_mu"].numpy(), st["k_scale"].numpy()), kq)

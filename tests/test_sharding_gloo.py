@@ -48,6 +48,52 @@ def _worker(rank, world, port, interleaved, result_path):
     dist.destroy_process_group()
 
 
+def _gather_worker(rank, world, port, backend, result_path):
+    """Equal shards into a persistent output buffer (the single-collective path) and ragged shards, on `backend`."""
+    sys.path.insert(0, os.path.join(ROOT, "int8-kvcache_b200"))
+    if backend == "nccl":
+        torch.cuda.set_device(rank)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank) if backend == "nccl" else torch.device("cpu")
+    dist.init_process_group(backend, init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    ok = True
+    for rows in ([3] * world, [2 + k for k in range(world)]):
+        gen = torch.Generator().manual_seed(5)
+        full = torch.randn(sum(rows), 4, 8, generator=gen).to(torch.bfloat16)
+        start = sum(rows[:rank])
+        local = full[start:start + rows[rank]].to(dev).contiguous()
+        out = torch.full((sum(rows), 4, 8), 7.0, dtype=torch.bfloat16, device=dev)
+        got = sharding.gather_outputs(local, rows, out=out)
+        ok = ok and got.data_ptr() == out.data_ptr() and torch.equal(out.cpu(), full)
+        ok = ok and torch.equal(sharding.gather_outputs(local, rows).cpu(), full)
+    try:
+        sharding.gather_outputs(local, [1] * world)
+        ok = False
+    except ValueError:
+        pass
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        np.save(result_path, int(flag.item()))
+    dist.destroy_process_group()
+
+
+def test_gather_outputs_gloo(tmp_path):
+    path = str(tmp_path / "ok.npy")
+    mp.spawn(_gather_worker, args=(2, _free_port(), "gloo", path), nprocs=2, join=True)
+    assert int(np.load(path)) == 1
+
+
+@pytest.mark.gpu
+def test_gather_outputs_nccl(tmp_path):
+    """The same gather over NCCL between two GPUs of the node (skipped on a single-GPU box)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    path = str(tmp_path / "ok.npy")
+    mp.spawn(_gather_worker, args=(2, _free_port(), "nccl", path), nprocs=2, join=True)
+    assert int(np.load(path)) == 1
+
+
 @pytest.mark.parametrize("interleaved", [False, True])
 def test_sharded_attention_equals_unsharded(tmp_path, interleaved):
     path = str(tmp_path / "diff.npy")

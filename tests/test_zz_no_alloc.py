@@ -3,8 +3,10 @@
 It serves callers that cannot allocate device memory (all HBM already given to the KV pool, code running under
 someone else's allocator or graph capture), so it keeps its scratch in a fixed array inside the library. Here it
 is compared with the regular entry point, which gets a workspace from the caller: same kernels, so the outputs
-must agree (checked with the tolerance the other GPU tests use; bit-equal for single-token decode). Two calls in a row
-with different batches make sure stale contents of the shared array do not leak into the next call.
+must agree (checked with the tolerance the other GPU tests use; bit-equal for single-token decode), and with the
+CPU oracle directly: for multi-token queries the built-in scratch only fits the layout with one m tile per work
+item, a mode of the kernel that no other caller reaches. Several calls in a row with different batches make sure
+stale contents of the shared array do not leak into the next call.
 
 This file sorts last on purpose: if it fails under `pytest -x`, every other test has already run.
 """
@@ -13,6 +15,7 @@ import ctypes
 import numpy as np
 import pytest
 import torch
+from gpu_util import assert_close, oracle_attention
 
 from kvq_b200 import _native
 from kvq_b200 import workloads
@@ -51,7 +54,10 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
     # two different batches back to back: a long single request cut over many CTAs (many partials left in the
     # scratch), then a ragged short-query batch that reuses the same array
     cases = [workloads.paged_case(61, 28, 4, 128, [1], [12000]),
-             workloads.paged_case(62, 28, 4, 128, [1, 5, 8, 1, 3], [700, 90, 2500, 33, 1024], q_std=3.0)]
+             workloads.paged_case(62, 28, 4, 128, [1, 5, 8, 1, 3], [700, 90, 2500, 33, 1024], q_std=3.0),
+             # verification batch in the shape of benchmark configuration 3: q_len 8, ragged contexts of 1k..8k
+             workloads.paged_case(64, 28, 4, 128, [8] * 12, [1024, 8192, 3000, 5555, 2049, 7000, 1500, 4096, 6100, 2500,
+                                                              7777, 1100])]
     for cpu_case in cases:
         case = _to_device(cpu_case)
         n = case["cu_seqlens_q"].numel() - 1
@@ -68,6 +74,7 @@ def test_noalloc_entry_point_matches_workspace_entry_point():
         # (multi-token queries: the workspace entry point lets warps share K/V streams across m tiles, the built-in
         #  scratch is too small for that mode's partials, so the summation order differs in the last fp32 bits)
         assert ref.abs().sum() > 0
+        assert_close(oracle_attention(cpu_case), out.float().cpu().numpy(), "no-alloc entry point vs oracle")
 
 
 def test_noalloc_rejects_batches_beyond_the_builtin_scratch():

@@ -1,12 +1,15 @@
 // INT8 paged attention for short queries (decode and speculative-decoding verification) on sm_100a.
 //
-// Three launches per call, all on the caller's stream, no host synchronization:
-//   plan_kernel     one block: per-request work in 32-key units, exclusive prefix sum, units per CTA
-//   decode_kernel   one CTA per slice of the global unit range (the range is cut evenly over
-//                   #SMs x resident CTAs, so every CTA streams the same number of KV bytes whatever the
-//                   mix of context lengths); a slice covers whole (request, kv head, m-tile group) items and at
-//                   most two partial ones, whose (acc, max, sum) go to the workspace
-//   merge_kernel    items that were cut across CTAs: combine their partials into the output
+// Two launches per call (three for batches of more than FUSED_PLAN_MAX requests), all on the caller's stream, no host
+// synchronization:
+//   decode_kernel   one CTA per slice of the global unit range (a unit is one 32-key chunk of one item; the range is
+//                   cut evenly over #SMs x resident CTAs, so every CTA streams the same number of KV bytes whatever
+//                   the mix of context lengths); a slice covers whole (request, kv head, m-tile group) items and at
+//                   most two partial ones, whose (acc, max, sum) go to the workspace. Every CTA sums the per-request
+//                   work itself to find its slice (a block scan over the requests instead of a kernel boundary)
+//   merge_kernel    items that were cut across CTAs: combine their partials into the output; folds the CTAs' status
+//   plan_kernel     large batches only, first: per-request units and their exclusive prefix sum in the workspace, so
+//                   that hundreds of CTAs do not each walk thousands of requests
 //
 // Inside decode_kernel the four warps of a CTA form groups of 1, 2 or 4 (per request, by its number of 16-row
 // m tiles). A group owns a slice of the TMA ring (cp.async.bulk.tensor, 128-byte swizzle, one 16-key x head_dim
@@ -32,7 +35,7 @@ namespace {
 constexpr int CHUNK = 32;      // keys per pipeline stage and per P-quantization tile
 constexpr int NWARPS = 4;
 constexpr int NTHREADS = NWARPS * 32;
-constexpr int NSTAGE = 3;      // TMA ring depth per warp
+constexpr int FUSED_PLAN_MAX = 1024;  // up to this many requests every CTA sums the work itself; beyond, plan_kernel runs first
 constexpr int MIN_UNITS = 4;   // never give a CTA less than one chunk per warp
 constexpr int MAX_CTAS_PER_SM = 4;
 constexpr int HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total units, [2] units per CTA
@@ -45,7 +48,8 @@ struct DecodeArgs {
   const int32_t *cu_q, *seq_lens, *block_table;
   const float *ks, *vs;
   int32_t* hdr;
-  const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units
+  const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units (only when planned)
+  int32_t* cta_status;     // [grid] 1 where a bounded wait of that CTA expired (folded into hdr[0] by the merge kernel)
   int32_t* bnd;            // [grid][8] what the end of each CTA's range cut (written by decode, read by merge)
   float* part_acc;         // [grid * 2][16][D]  numerator * v_scale of a cut item
   float* part_ml;          // [grid * 2][16][2]  running max of the scores, denominator
@@ -53,6 +57,7 @@ struct DecodeArgs {
   int num_seqs, Hq, Hkv, G, lbs, bs_mask, qmax;
   int64_t q_st, q_sh, o_st, o_sh, bt_stride;
   int pc_k, pc_v;
+  int planned;             // 1: plan_kernel ran first (large batches); 0: every CTA derives its slice itself
   int grouped;             // 1: warps of a CTA share K/V streams across m tiles (multi-token queries)
   int hg;                  // 0, or 2 / 4: decode with warps of a group on ADJACENT KV HEADS of one stream (see req_shape)
   int part_rows;           // rows per partial slot: 16, or 64 in grouped mode
@@ -148,7 +153,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
   __shared__ int s_carry;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_launch_dependents();   // the attention kernel may set itself up while the plan is computed
-  if (tid == 0) s_carry = 0, hdr[0] = 0;
+  if (tid == 0) s_carry = 0;
   __syncthreads();
   for (int base = 0; base < num_seqs; base += 256) {
     const int r = base + tid;
@@ -189,12 +194,17 @@ __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ c
 // four m tiles. Groups that worked on the same m tile are combined through shared memory at the end of an item.
 template <int D, bool ROWS16>
 struct Geom {
+  // The 16-row variant (multi-token queries) is bound by its instruction stream at two register-limited warps per
+  // scheduler, not by HBM: it runs three CTAs per SM (168 registers per thread) on a ring of two stages per warp,
+  // which keeps the same number of bytes in flight per SM as the 8-row decode variant's two CTAs of three stages.
+  static constexpr int NSTAGE = ROWS16 ? 2 : 3;   // TMA ring depth per warp
+  static constexpr int MIN_CTAS = ROWS16 ? 3 : 2; // resident CTAs per SM the kernel is compiled for
   static constexpr int TILE = CHUNK * D;          // one K or V chunk
   static constexpr int STAGE = 2 * TILE;          // K chunk + V chunk
   static constexpr int NSTG = NWARPS * NSTAGE;    // stages per CTA
   static constexpr int RING = NSTG * STAGE;
   static constexpr int SLOTS = NWARPS;            // m tiles (or kv heads of a head group) a CTA holds q for
-  static constexpr int QROW = D + 16;             // s_q row stride: conflict-free A-fragment loads
+  static constexpr int QROW = D;                  // s_q row stride (read once per item: bank conflicts do not matter)
   static constexpr int ACC_RS = D + 8;            // combine buffer row stride in floats
   static constexpr int SMALL = SLOTS * 16 * QROW + 6 * 64 * 4;
   static constexpr int SMEM = 1024 + RING + SMALL;  // 1024: manual alignment of the ring
@@ -208,7 +218,7 @@ struct Geom {
 template <int D>
 __device__ __forceinline__ void q_quantize_row(const DecodeArgs& a, uint2 raw, const float (&sk)[4], int8_t* s_q,
                                                float* s_chi, float* s_clo, int kvh, int row, int lane) {
-  constexpr int QROW = D + 16, LANES = D / 4;
+  constexpr int QROW = D, LANES = D / 4;
   const bool lane_on = lane < LANES;
   const int d0 = (lane_on ? lane : 0) * 4;
   float x[4] = {bf16lo(raw.x), bf16hi(raw.x), bf16lo(raw.y), bf16hi(raw.y)};
@@ -328,8 +338,25 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 // like the reference's float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100
 // that moves P = exp(score - max) by 1e-5 and flips its int8 quantization far more often than the reference's own
 // noise. nhi = -hi (packed pair).
+//
+// MAGIC (the 16-row variant): the int32 accumulators of the mma start at the bit pattern of 1.5 * 2^23 instead of zero, so
+// the accumulated integer read as a float is 12582912 + dot exactly (|dot| < 2^22: at most 128 x 127 x 127), and one packed
+// subtraction per pair replaces two int -> float conversions. The 8-row decode variant keeps the conversions: it runs at the
+// pace of the memory system and its instruction stream is left as it is.
+constexpr int MAGIC_BITS = 0x4B400000;
+constexpr float MAGIC_F = 12582912.f;
+template <bool MAGIC>
+__device__ __forceinline__ f32x2 ints_to_f32x2(int d0, int d1) {
+  if (MAGIC) {
+    f32x2 r;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(pk2(__int_as_float(d0), __int_as_float(d1))), "l"(pk2(MAGIC_F, MAGIC_F)));
+    return r;
+  }
+  return pk2(static_cast<float>(d0), static_cast<float>(d1));
+}
+template <bool MAGIC>
 __device__ __forceinline__ void score2(int d0, int d1, f32x2 hi, f32x2 nhi, f32x2 lo, float& s0, float& s1) {
-  const f32x2 d = pk2(static_cast<float>(d0), static_cast<float>(d1));
+  const f32x2 d = ints_to_f32x2<MAGIC>(d0, d1);
   const f32x2 pn = mul2(d, nhi);                       // -(d * hi), rounded
   upk2(sub2(fma2(d, lo, fma2(d, hi, pn)), pn), s0, s1);   // p + (d * lo + (d * hi - p))
 }
@@ -354,7 +381,7 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   int sacc[4][4];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
+    sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = ROWS16 ? MAGIC_BITS : 0;
 #pragma unroll
     for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
       uint32_t b[4];
@@ -371,8 +398,8 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
   const f32x2 hi1 = pk2(s.ch1, s.ch1), nhi1 = pk2(-s.ch1, -s.ch1), lo1 = pk2(s.cl1, s.cl1);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    score2(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
-    if (ROWS16) score2(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
+    score2<ROWS16>(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
+    if (ROWS16) score2<ROWS16>(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int n = n_base + 8 * j + 2 * t + e;
@@ -440,27 +467,28 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
     ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp, hs, hsel));
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
-      int pacc[4] = {0, 0, 0, 0};
+      int pacc[4];
+      pacc[0] = pacc[1] = pacc[2] = pacc[3] = ROWS16 ? MAGIC_BITS : 0;
       mma_s8(pacc, pa, b[h2], b[2 + h2]);
       float* o = s.acc[2 * jp + h2];
       // (o0, o1) = (x0, x1) * ps + (o0, o1) * al
-      upk2(fma2(pk2(static_cast<float>(pacc[0]), static_cast<float>(pacc[1])), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
+      upk2(fma2(ints_to_f32x2<ROWS16>(pacc[0], pacc[1]), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
       if (ROWS16)
-        upk2(fma2(pk2(static_cast<float>(pacc[2]), static_cast<float>(pacc[3])), ps1_2, mul2(pk2(o[2], o[3]), al1_2)), o[2], o[3]);
+        upk2(fma2(ints_to_f32x2<ROWS16>(pacc[2], pacc[3]), ps1_2, mul2(pk2(o[2], o[3]), al1_2)), o[2], o[3]);
     }
   }
 }
 
 template <int D, bool ROWS16>
-__global__ void __launch_bounds__(NTHREADS, 2)
+__global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
     decode_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
   using Gm = Geom<D, ROWS16>;
-  constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS, NSTG = Gm::NSTG;
+  constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS, NSTG = Gm::NSTG, NSTAGE = Gm::NSTAGE;
   constexpr int NROWS = ROWS16 ? 16 : 8;
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[NSTG];    // TMA landed in the stage
   __shared__ __align__(8) uint64_t s_empty[NSTG];   // every warp of the group is done with the stage
-  __shared__ int s_req;
+  __shared__ int s_req, s_p0, s_scan[NWARPS];
 
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
@@ -482,12 +510,59 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   fence_proxy_async();   // ordered before the first TMA issue by the __syncthreads of the request search below
   pdl_wait();            // everything above overlapped the plan kernel; its results are read from here on
   pdl_launch_dependents();
-  const int total = a.hdr[1], W = a.hdr[2];
-  const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
-  if (ubeg >= uend) {
-    if (tid == 0) a.bnd[blockIdx.x * 8] = -1;   // nothing is cut at the end of an empty range
-    return;
+  // ---- this CTA's slice [ubeg, uend) of the global unit range and the request that owns its first unit ----
+  int total, W;
+  if (a.planned) {   // large batches: plan_kernel left the prefix sums of the per-request units
+    total = a.hdr[1], W = a.hdr[2];
+    const int ub = blockIdx.x * W;
+    if (ub < total)
+      for (int r = tid; r < a.num_seqs; r += NTHREADS)
+        if (a.prefix[r] <= ub && ub < a.prefix[r + 1]) s_req = r, s_p0 = a.prefix[r];
+  } else {
+    // every CTA sums the units itself: thread t takes a contiguous run of requests, the runs are scanned over the
+    // block, and the thread whose run contains the CTA's first unit walks it again to find the request
+    const int per = (a.num_seqs + NTHREADS - 1) / NTHREADS;
+    const int r0 = tid * per, r1 = min(a.num_seqs, r0 + per);
+    auto units_of = [&](int r) {
+      return req_shape(a.cu_q[r + 1] - a.cu_q[r], a.seq_lens[r], a.G, a.Hkv, a.qmax, a.grouped, a.hg).units;
+    };
+    int local = 0;
+    for (int r = r0; r < r1; ++r) local += units_of(r);
+    int x = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) s_scan[warp] = x;
+    __syncthreads();
+    int woff = 0;
+    total = 0;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      if (w < warp) woff += s_scan[w];
+      total += s_scan[w];
+    }
+    W = max((total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), MIN_UNITS);
+    if (blockIdx.x == 0 && tid == 0) a.hdr[1] = total, a.hdr[2] = W;   // for the merge kernel
+    const int ub = blockIdx.x * W, excl = woff + x - local;
+    if (ub < total && excl <= ub && ub < excl + local) {
+      int p = excl;
+      for (int r = r0; r < r1; ++r) {
+        const int ur = units_of(r);
+        if (ub < p + ur) {
+          s_req = r, s_p0 = p;
+          break;
+        }
+        p += ur;
+      }
+    }
   }
+  const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
+  // defaults: nothing is cut at the end of this CTA's range, no wait expired (overwritten below where that changes)
+  if (tid == 0) a.bnd[blockIdx.x * 8] = -1, a.cta_status[blockIdx.x] = 0;
+  if (ubeg >= uend) return;
+  __syncthreads();
 
   // Lane-constant pieces of the ldmatrix addresses.
   // K (non-transposed, 4 matrices of 8 keys x 16 channels): lane l addresses key (l & 7) of matrix l >> 3.
@@ -501,16 +576,16 @@ __global__ void __launch_bounds__(NTHREADS, 2)
   bool ok = true;
   int u = ubeg;
   bool first_seg = true;
-  while (u < uend) {
-    // ---- find the request that owns unit u: prefix[r] <= u < prefix[r + 1] ----
-    for (int r = tid; r < a.num_seqs; r += NTHREADS)
-      if (a.prefix[r] <= u && u < a.prefix[r + 1]) s_req = r;
-    __syncthreads();
-    const int req = s_req;
+  int req = s_req, p0 = s_p0;   // the request that owns unit u and its first unit; later requests follow in order
+  while (u < uend && req < a.num_seqs) {
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
     const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, a.hg);
+    if (rs.units == 0) {   // padding (q_len 0) and long requests have no work here
+      ++req;
+      continue;
+    }
     const int nchunks = rs.nchunks;
-    const int p0 = a.prefix[req], p1 = a.prefix[req + 1];
+    const int p1 = p0 + rs.units;
     const int32_t* bt = a.block_table + static_cast<int64_t>(req) * a.bt_stride;
 
     // ---- warp groups for this request; the ring and its barriers are re-partitioned when the group size changes
@@ -670,7 +745,7 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         if (GS > 1 && lane == 0) mbar_arrive(gempty + st * 8);
         if (++cst == RD) cst = 0, ++cpass;
       }
-      if (!ok) atomicExch(a.hdr, 1);
+      if (!ok) a.cta_status[blockIdx.x] = 1;
 
       // -- combine the warps that worked on the same m tile (slot msl of every group): weights exp(m_w - M) --
       if (t == 0) {
@@ -754,6 +829,8 @@ __global__ void __launch_bounds__(NTHREADS, 2)
         }
       }
     }
+    ++req;
+    p0 = p1;
   }
 }
 
@@ -780,6 +857,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   __shared__ float4 s_num[PG][LPP];
   __shared__ float s_den[PG];
   pdl_wait();   // the records and partials below are written by the attention kernel
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x < 32) {
+    // status word of the call: 1 if a bounded wait expired in any CTA of the attention kernel
+    int bad = 0;
+    for (int c = threadIdx.x; c <= static_cast<int>(gridDim.x); c += 32) bad |= a.cta_status[c];
+    bad = __any_sync(0xffffffffu, bad != 0);
+    if (threadIdx.x == 0) a.hdr[0] = bad;
+  }
   const int4 r0 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8);
   if (r0.x < 0) return;
   const int4 r1 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8 + 4);
@@ -1012,13 +1096,14 @@ cudaEvent_t g_ev_start = nullptr, g_ev_stop = nullptr;  // optional profiling br
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t prefix, bnd, part_acc, part_ml, total;
+  size_t prefix, bnd, status, part_acc, part_ml, total;
 };
 WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas, int part_rows) {
   WorkspaceLayout w;
   w.prefix = HDR_BYTES;
   w.bnd = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
-  w.part_acc = w.bnd + align_up(static_cast<size_t>(max_ctas) * 32, 256);
+  w.status = w.bnd + align_up(static_cast<size_t>(max_ctas) * 32, 256);
+  w.part_acc = w.status + align_up(static_cast<size_t>(max_ctas) * 4, 256);
   w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * part_rows * D * 4;
   w.total = w.part_ml + static_cast<size_t>(max_ctas) * 2 * part_rows * 2 * 4;
   return w;
@@ -1119,6 +1204,8 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
   a.hdr = reinterpret_cast<int32_t*>(ws);
   a.prefix = reinterpret_cast<const int32_t*>(ws + wl.prefix);
   a.bnd = reinterpret_cast<int32_t*>(ws + wl.bnd);
+  a.cta_status = reinterpret_cast<int32_t*>(ws + wl.status);
+  a.planned = num_seqs > FUSED_PLAN_MAX;
   a.part_acc = reinterpret_cast<float*>(ws + wl.part_acc);
   a.part_ml = reinterpret_cast<float*>(ws + wl.part_ml);
   a.sm_hi = static_cast<float>(softmax_scale);
@@ -1139,8 +1226,9 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     return rc;
 
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, grid, a.hdr,
-                                reinterpret_cast<int32_t*>(ws + wl.prefix));
+  if (a.planned)
+    plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, grid, a.hdr,
+                                  reinterpret_cast<int32_t*>(ws + wl.prefix));
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   if (head_dim == 128) {
     if (rows16)
@@ -1148,14 +1236,14 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     else
       KVQ_CUDA(launch_pdl(decode_kernel<128, false>, dim3(grid), dim3(NTHREADS), Geom<128, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(grid - 1, 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(std::max(grid - 1, 1), 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
   } else {
     if (rows16)
       KVQ_CUDA(launch_pdl(decode_kernel<64, true>, dim3(grid), dim3(NTHREADS), Geom<64, true>::SMEM, s, a, tm_k, tm_v));
     else
       KVQ_CUDA(launch_pdl(decode_kernel<64, false>, dim3(grid), dim3(NTHREADS), Geom<64, false>::SMEM, s, a, tm_k, tm_v));
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    if (grid > 1) KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(grid - 1, 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(std::max(grid - 1, 1), 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
   }
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;

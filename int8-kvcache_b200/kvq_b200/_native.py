@@ -6,7 +6,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libkvq_b200.so")
+# KVQ_B200_LIB points at another build of the same library (e.g. an installed copy); default: the in-tree build
+LIB_PATH = os.environ.get("KVQ_B200_LIB") or os.path.join(os.path.dirname(_HERE), "lib", "libkvq_b200.so")
 
 _c_i64, _c_int, _c_ptr = ctypes.c_int64, ctypes.c_int, ctypes.c_void_p
 

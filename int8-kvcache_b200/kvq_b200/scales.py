@@ -98,5 +98,41 @@ def merge_tp(per_rank, num_kv_heads):
             if field != "tokens":
                 merged[field] = torch.cat([p[field] for p in per], dim=0)
         stats[layer] = merged
-        samples[layer] = {side: torch.cat([r["samples"][layer][side] for r in ranks], dim=1) for side in ("k", "v")}
+        if all(layer in r["samples"] for r in ranks):   # sampled rows are optional (quantile scales only)
+            samples[layer] = {side: torch.cat([r["samples"][layer][side] for r in ranks], dim=1) for side in ("k", "v")}
     return stats, samples
+
+
+# The scale-file variants a calibration run writes, as (granularity, method, smooth_k)
+# (the six of the reference's scripts/calibrate.py:23-26).
+CALIBRATION_VARIANTS = (("per_channel", "max", False), ("per_channel", "max", True), ("per_channel", "q0.999", True),
+                        ("per_channel", "q0.9999", True), ("per_head", "max", False), ("per_head", "max", True))
+
+
+def variant_file_name(prefix, granularity, method, smooth_k):
+    """<prefix>_<granularity>_<method>[_smooth].safetensors, the naming of the reference's scale files
+    (e.g. math_per_channel_max_smooth.safetensors)."""
+    return f"{prefix}_{granularity}_{method}{'_smooth' if smooth_k else ''}.safetensors"
+
+
+def calibrate_from(per_rank, num_kv_heads, out_dir, prefix="calib", variants=CALIBRATION_VARIANTS):
+    """From what every tensor-parallel rank's capture.collect() returned to one scale file per variant in out_dir
+    (the second half of the reference's scripts/calibrate.py:59-76; the first half, running a calibration set through
+    the engine with KVQ_CAPTURE=1, belongs to the serving stack). Quantile variants need the sampled rows and are
+    skipped for layers without samples. Returns {"tokens": rows seen by the first layer, "variants": [file names]}."""
+    import os
+
+    stats, samples = merge_tp(per_rank, num_kv_heads)
+    if not stats:
+        raise ValueError("calibrate_from: the capture holds no layer statistics (was KVQ_CAPTURE=1 set before the run?)")
+    os.makedirs(out_dir, exist_ok=True)
+    written = []
+    for granularity, method, smooth_k in variants:
+        needs_samples = method != "max"
+        if needs_samples and any(name not in samples for name in stats):
+            continue
+        layer_scales = {name: from_stats(stats[name], samples.get(name), granularity, method, smooth_k) for name in stats}
+        name = variant_file_name(prefix, granularity, method, smooth_k)
+        save(os.path.join(out_dir, name), layer_scales)
+        written.append(name)
+    return {"tokens": int(next(iter(stats.values()))["tokens"]), "variants": written}

@@ -49,22 +49,22 @@ def digest(*tensors):
     return h.hexdigest()
 
 
-def ref_attention(case, per_channel=True, smooth=False, fp32=True):
-    cfg = Cfg(smooth_k=smooth, p_tile=32) if per_channel else Cfg(smooth_k=smooth, p_tile=32, k_gran="per_head",
-                                                                   v_gran="per_head")
+def ref_attention(case, per_channel=True, smooth=False, fp32=True, q_gran="token_head"):
+    cfg = (Cfg(smooth_k=smooth, p_tile=32, q_gran=q_gran) if per_channel else
+           Cfg(smooth_k=smooth, p_tile=32, k_gran="per_head", v_gran="per_head", q_gran=q_gran))
     fn = paged_static_attention(cfg, case["static"], cache_is_int8=True, short_q=8)
     q = case["q"].float() if fp32 else case["q"]
     return fn(q, case["kq"], case["vq"], case["cu_seqlens_q"], case["seq_lens"], case["block_table"],
               case["softmax_scale"])
 
 
-def save_attention(name, case, per_channel, smooth, store_inputs=True, with_bf16_golden=False):
+def save_attention(name, case, per_channel, smooth, store_inputs=True, with_bf16_golden=False, q_gran="token_head"):
     # the workload generator's cache filler must agree with the reference's quantizer bit for bit
     st = case["static"]
     assert torch.equal(case["kq"], ref_quant.quantize(case["k"].float() - st["k_mu"], st["k_scale"]))
     assert torch.equal(case["vq"], ref_quant.quantize(case["v"], st["v_scale"]))
-    out = {"ref_out": ref_attention(case, per_channel, smooth).numpy(),
-           "ref_out_bf16": bits(ref_attention(case, per_channel, smooth, fp32=False)),
+    out = {"ref_out": ref_attention(case, per_channel, smooth, q_gran=q_gran).numpy(),
+           "ref_out_bf16": bits(ref_attention(case, per_channel, smooth, fp32=False, q_gran=q_gran)),
            "input_sha256": np.array(digest(case["q"], case["kq"], case["vq"], case["block_table"]))}
     if with_bf16_golden:
         out["bf16_golden"] = paged_attention_ref(case["q"].float(), case["k"], case["v"], case["cu_seqlens_q"],
@@ -172,6 +172,18 @@ def save_calib():
 
 def main():
     torch.manual_seed(0)
+    only = sys.argv[1:]   # fixture names to (re)generate; default: all
+    if only:
+        import builtins
+        real_savez = np.savez_compressed
+
+        def filtered(path, **kw):
+            if os.path.basename(path) in only:
+                real_savez(path, **kw)
+            else:
+                builtins.print("  (not rewritten)", end=" ")
+
+        np.savez_compressed = filtered
     save_attention("attn_config0.npz", workloads.config0(), True, False, store_inputs=False, with_bf16_golden=True)
     save_attention("attn_short_smooth.npz",
                    workloads.paged_case(21, 12, 2, 128, [2, 8, 1, 5, 3], [40, 200, 129, 96, 8], num_blocks=40,
@@ -181,6 +193,14 @@ def main():
                                         per_channel=False, smooth=True), False, True)
     save_attention("attn_mixed_long.npz",
                    workloads.paged_case(23, 12, 2, 128, [1, 33, 4, 9], [50, 100, 31, 70], num_blocks=24), True, False)
+    # the reference's CONFIGS["B_channel_smooth_qgroup32"] (kvq/int8_ref.py:220) with the kernel's 32-key P tile, and the
+    # same with per-head K/V scales
+    save_attention("attn_qgroup32.npz",
+                   workloads.paged_case(24, 12, 2, 128, [1, 8, 3, 1, 5], [300, 77, 1030, 16, 150], num_blocks=110,
+                                        smooth=True, q_std=3.0), True, True, q_gran="group32")
+    save_attention("attn_qgroup32_per_head.npz",
+                   workloads.paged_case(25, 28, 4, 128, [1, 2, 7], [100, 513, 40], num_blocks=48, per_channel=False,
+                                        smooth=True, q_std=3.0), False, True, q_gran="group32")
     for d in (128, 64):
         for pc in (True, False):
             save_write(f"write_d{d}_{'channel' if pc else 'head'}.npz", d, pc)

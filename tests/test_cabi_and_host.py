@@ -212,3 +212,165 @@ def test_short_q_is_one_threshold_everywhere():
     res = run("4")
     assert res.stdout.split(None, 3) == ["4", "8", "0", "[0, 0, 0, 1, 1, 1, 1]\n"], res.stdout
     assert run("0").returncode != 0
+
+
+# ---------------------------------------------------------------------------------------------------
+# vLLM glue without an engine: scale hand-out, cache dtype registration, capture hook, calibration files
+# ---------------------------------------------------------------------------------------------------
+class _FakeImpl:
+    """Stands in for a layer's Int8StaticImpl: records what set_static receives, completed like the real one."""
+
+    def __init__(self, num_kv_heads, head_size=8):
+        self.num_kv_heads, self.head_size, self.static = num_kv_heads, head_size, None
+
+    def set_static(self, static):
+        from kvq_b200.vllm_int8 import backend as b
+
+        self.static = b.complete_static(static, self.num_kv_heads, self.head_size)
+
+
+def _layer_table(layers, heads=4, dim=8, with_mu=True, offset=0.0):
+    table = {}
+    for i in range(layers):
+        base = torch.arange(heads * dim, dtype=torch.float32).reshape(heads, dim) + 100 * i + offset
+        table[f"model.layers.{i}.self_attn.attn"] = {"k_scale": base + 1, "v_scale": base + 2,
+                                                     **({"k_mu": base + 3} if with_mu else {})}
+    return table
+
+
+def test_builder_hands_every_layer_its_rank_slice(tmp_path):
+    """What Int8StaticBuilder.__init__ does with the scale files (reference: kvq/vllm_int8/backend.py:90-105): every
+    layer gets its tensor-parallel rows; layers the target file does not know come from the draft file, looked up
+    without the draft prefix; files without k_mu get zeros; replicated kv heads follow the replica rule."""
+    pytest.importorskip("vllm")
+    from kvq_b200.vllm_int8 import backend as b
+
+    main_path, draft_path = str(tmp_path / "main.safetensors"), str(tmp_path / "draft.safetensors")
+    scales.save(main_path, _layer_table(3))
+    scales.save(draft_path, _layer_table(1, with_mu=False, offset=0.5))
+    files = b.ScaleFiles.from_env({"KVQ_SCALES": main_path, "KVQ_DRAFT_SCALES": draft_path})
+    names = [f"model.layers.{i}.self_attn.attn" for i in range(3)] + ["draft_model.model.layers.0.self_attn.attn"]
+    for tp_size, rows in ((1, 4), (2, 2), (4, 1), (8, 1)):
+        for rank in range(tp_size):
+            impls = {n: _FakeImpl(rows) for n in names}
+            drafted = b.assign_layer_scales(impls.__getitem__, names, files, rank, tp_size, torch.device("cpu"))
+            assert drafted == 1
+            full = _layer_table(3)
+            for i in range(3):
+                got, want = impls[names[i]].static, full[names[i]]
+                for field in ("k_scale", "v_scale", "k_mu"):
+                    assert torch.equal(got[field], scales.shard(want[field], rank, tp_size)), (tp_size, rank, field)
+                    assert got[field].dtype == torch.float32 and got[field].is_contiguous()
+            d = impls[names[3]].static
+            assert torch.equal(d["k_scale"], scales.shard(_layer_table(1, offset=0.5)[names[0]]["k_scale"], rank, tp_size))
+            assert d["k_mu"].shape == (rows, 8) and not d["k_mu"].any()          # no smooth-K in the draft file
+    with pytest.raises(ValueError, match="kv heads"):
+        _FakeImpl(3).set_static(scales.for_layer(_layer_table(1), names[0], 0, 1, "cpu"))
+    with pytest.raises(KeyError):
+        b.assign_layer_scales({"other.layer": _FakeImpl(4)}.__getitem__, ["other.layer"], files, 0, 1, "cpu")
+    with pytest.raises(RuntimeError, match="KVQ_SCALES"):
+        b.ScaleFiles.from_env({})
+
+
+def test_graph_support_level_follows_the_short_query_limit():
+    pytest.importorskip("vllm")
+    from vllm.v1.attention.backend import AttentionCGSupport
+    from kvq_b200.vllm_int8 import backend as b
+
+    assert b.graph_support_level(0, AttentionCGSupport) == AttentionCGSupport.UNIFORM_BATCH
+    assert b.graph_support_level(ck.SHORT_Q - 1, AttentionCGSupport) == AttentionCGSupport.UNIFORM_BATCH
+    assert b.graph_support_level(ck.SHORT_Q, AttentionCGSupport) == AttentionCGSupport.UNIFORM_SINGLE_TOKEN_DECODE
+
+    class Cfg:   # what the builder classmethod reads from vllm_config
+        class speculative_config:
+            num_speculative_tokens = 3
+
+    assert b.Int8StaticBuilder.get_cudagraph_support(Cfg, None) == AttentionCGSupport.UNIFORM_BATCH
+    Cfg.speculative_config = None
+    assert b.Int8StaticBuilder.get_cudagraph_support(Cfg, None) == AttentionCGSupport.UNIFORM_BATCH
+
+
+def test_plugin_registers_backend_and_cache_dtype():
+    """register() in a fresh interpreter (it edits vLLM's config classes): the CUSTOM backend resolves to this
+    package's class and an unpatched vLLM accepts kv_cache_dtype="int8_static" as an int8 cache."""
+    pytest.importorskip("vllm")
+    import subprocess
+    import sys
+
+    code = (
+        "import sys; sys.path.insert(0, %r)\n"
+        "from kvq_b200 import vllm_plugin\n"
+        "vllm_plugin.register(); vllm_plugin.register()\n"
+        "import torch\n"
+        "from vllm.config.cache import CacheConfig\n"
+        "from vllm.utils.torch_utils import STR_DTYPE_TO_TORCH_DTYPE\n"
+        "from vllm.v1.attention.backends.registry import AttentionBackendEnum\n"
+        "assert CacheConfig(cache_dtype='int8_static').cache_dtype == 'int8_static'\n"
+        "assert STR_DTYPE_TO_TORCH_DTYPE['int8_static'] is torch.int8\n"
+        "cls = AttentionBackendEnum.CUSTOM.get_class()\n"
+        "assert cls.__name__ == 'Int8StaticBackend' and cls.supports_kv_cache_dtype('int8_static')\n"
+        "print('registered')\n"
+    ) % os.path.join(ROOT, "int8-kvcache_b200")
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True)
+    assert res.returncode == 0 and "registered" in res.stdout, res.stderr[-2000:]
+
+
+def test_capture_hook_wraps_the_cache_update(monkeypatch):
+    """capture.install() against a stand-in for vLLM's FlashAttentionImpl (the reference's hook,
+    kvq/capture.py:87-106): the original update still runs, with the same arguments, after the rows are recorded."""
+    import sys
+    import types
+
+    from kvq_b200 import capture
+
+    calls = []
+
+    class FlashAttentionImpl:
+        def do_kv_cache_update(self, layer, key, value, kv_cache, slot_mapping):
+            calls.append(("orig", layer.layer_name, key, value, kv_cache, slot_mapping))
+            return "written"
+
+    fake = types.ModuleType("vllm.v1.attention.backends.flash_attn")
+    fake.FlashAttentionImpl = FlashAttentionImpl
+    for name in ("vllm", "vllm.v1", "vllm.v1.attention", "vllm.v1.attention.backends"):
+        monkeypatch.setitem(sys.modules, name, sys.modules.get(name) or types.ModuleType(name))
+    monkeypatch.setitem(sys.modules, "vllm.v1.attention.backends.flash_attn", fake)
+    monkeypatch.setattr(capture, "record", lambda *a: calls.append(("record",) + a))
+    capture.install()
+    layer = types.SimpleNamespace(layer_name="model.layers.0.self_attn.attn")
+    assert FlashAttentionImpl().do_kv_cache_update(layer, "k", "v", "cache", "slots") == "written"
+    assert calls == [("record", "model.layers.0.self_attn.attn", "k", "v", "slots"),
+                     ("orig", "model.layers.0.self_attn.attn", "k", "v", "cache", "slots")]
+    del FlashAttentionImpl.do_kv_cache_update     # a backend without the method: loud failure, not a silent no-op
+    with pytest.raises(RuntimeError, match="do_kv_cache_update"):
+        capture.install()
+
+
+def test_calibrate_from_writes_the_six_variants(tmp_path):
+    """Per-rank capture results -> one scale file per (granularity, method, smooth) variant, merged over two
+    tensor-parallel ranks; file names follow the reference's scale files; quantile variants are skipped without
+    samples."""
+    gen = torch.Generator().manual_seed(3)
+    rows, heads, dim = 50, 2, 8
+
+    def rank_result(rank):
+        k = torch.randn(rows, heads, dim, generator=gen) * 2 + 1
+        v = torch.randn(rows, heads, dim, generator=gen)
+        st = {"tokens": rows, "k_absmax": k.abs().amax(0), "k_max": k.amax(0), "k_min": k.amin(0), "k_sum": k.double().sum(0),
+              "v_absmax": v.abs().amax(0), "v_max": v.amax(0), "v_min": v.amin(0), "v_sum": v.double().sum(0)}
+        return {"stats": {"L0": st}, "samples": {"L0": {"k": k.half(), "v": v.half()}}, "tp_rank": rank, "tp_size": 2}
+
+    per_rank = [rank_result(1), rank_result(0)]
+    summary = scales.calibrate_from(per_rank, num_kv_heads=4, out_dir=str(tmp_path), prefix="math")
+    assert summary["tokens"] == rows and len(summary["variants"]) == 6
+    assert "math_per_channel_max_smooth.safetensors" in summary["variants"]
+    assert "math_per_head_max.safetensors" in summary["variants"]
+    loaded = scales.load(str(tmp_path / "math_per_channel_max_smooth.safetensors"))["L0"]
+    assert loaded["k_scale"].shape == (4, dim) and loaded["k_mu"].shape == (4, dim)       # two ranks x two heads
+    by_rank = sorted(per_rank, key=lambda r: r["tp_rank"])
+    want = torch.cat([r["stats"]["L0"]["v_absmax"] for r in by_rank]) / 127.0
+    assert torch.allclose(loaded["v_scale"], want)
+    assert scales.load(str(tmp_path / "math_per_head_max.safetensors"))["L0"]["k_scale"].shape == (4, 1)
+    for r in per_rank:
+        r["samples"] = {}
+    assert len(scales.calibrate_from(per_rank, 4, str(tmp_path / "nosamples"))["variants"]) == 4

@@ -16,6 +16,10 @@ from oracle import kvq_oracle as orc
 
 pytestmark = pytest.mark.gpu
 
+DECODE = ([1] * 11, [1, 16, 17, 31, 32, 33, 250, 1023, 2049, 700, 3100])
+SHORT = ([2, 4, 8, 3, 1, 5, 7, 1, 6], [37, 650, 1025, 9, 2050, 100, 2800, 16, 513])
+MIXED = ([1, 1, 7, 40, 130, 1, 290, 9, 4, 0], [590, 33, 7, 480, 130, 1400, 910, 1900, 70, 12])
+
 def bf16_t(bits):
     return torch.from_numpy(bits.view(np.int16)).view(torch.bfloat16)
 
@@ -409,3 +413,36 @@ def test_cache_write_under_graph_capture_skips_padded_slots():
     orc.quant_cache_write(c["key"].float().numpy(), c["value"].float().numpy(), rk, rv, slots.cpu().numpy(),
                           s["k_scale"].numpy(), s["v_scale"].numpy(), s["k_mu"].numpy())
     assert np.array_equal(kc.cpu().numpy(), rk) and np.array_equal(vc.cpu().numpy(), rv)
+
+
+def test_large_batch_takes_the_planned_path():
+    """More requests than a CTA sums by itself (1024): the plan kernel runs first and the CTAs look their first
+    request up in its prefix sums. 1500 decode requests with short ragged contexts, padding requests in between."""
+    gen = torch.Generator().manual_seed(47)
+    n = 1500
+    ctx = torch.randint(1, 200, (n,), generator=gen).tolist()
+    q_lens = [0 if i % 97 == 5 else 1 for i in range(n)]
+    case = workloads.paged_case(47, 28, 4, 128, q_lens, ctx)
+    out = torch.full_like(case["q"], 7.0).to(DEV)
+    got = run_decode(case, out=out)
+    assert_close(oracle_attention(case), got, "planned path")
+
+
+def test_items_follow_each_other_without_draining_the_stream():
+    """Decode batch in which every CTA meets several items: many requests of a few chunks each, so that a warp's
+    stream runs across item and request boundaries (next item's pages and q rows are fetched while the current one
+    runs), including requests too short to give every warp a chunk and requests that are skipped."""
+    gen = torch.Generator().manual_seed(48)
+    n = 700
+    ctx = torch.randint(1, 700, (n,), generator=gen).tolist()
+    q_lens = [1] * n
+    for i in range(0, n, 41):
+        q_lens[i] = 0          # padding request
+    for i in range(7, n, 53):
+        q_lens[i] = 12         # long request: not this kernel's
+    case = workloads.paged_case(48, 28, 4, 128, q_lens, ctx, q_std=2.0)
+    out = torch.full_like(case["q"], 7.0).to(DEV)
+    got = run_decode(case, out=out, max_query_len=1)
+    short = short_row_mask(case)
+    assert (got[~short] == 7.0).all()
+    assert_close(oracle_attention(case)[short], got[short], "stream across items")

@@ -15,10 +15,22 @@ from oracle import kvq_oracle as orc
 ATTN_TOL = dict(max_abs=2e-4, mean_abs=5e-6)   # oracle vs reference, both fp32 evaluations
 
 
-def _attention_from_fixture(fx):
+def _attention_from_fixture(fx, q_group=None):
     q = orc.bf16_bits_to_f32(fx["q"])
     return orc.paged_static_attention(q, fx["kq"], fx["vq"], fx["cu_seqlens_q"], fx["seq_lens"], fx["block_table"],
-                                      float(fx["softmax_scale"]), fx["k_scale"], fx["v_scale"], short_q=8, p_tile=32)
+                                      float(fx["softmax_scale"]), fx["k_scale"], fx["v_scale"], short_q=8, p_tile=32,
+                                      q_group=q_group)
+
+
+@pytest.mark.parametrize("name", ["attn_qgroup32.npz", "attn_qgroup32_per_head.npz"])
+def test_group32_q_scales_match_reference(name):
+    """One q scale per 32-channel slice (the reference's q_gran="group32", kvq/int8_ref.py:120-130 and
+    CONFIGS["B_channel_smooth_qgroup32"]): fixtures made by the reference itself; and the option changes the result."""
+    fx = load_golden(name)
+    out = _attention_from_fixture(fx, q_group=32)
+    err = orc.compare(fx["ref_out"], out)
+    assert err["max_abs"] < ATTN_TOL["max_abs"] and err["mean_abs"] < ATTN_TOL["mean_abs"], err
+    assert orc.compare(fx["ref_out"], _attention_from_fixture(fx))["max_abs"] > 10 * err["max_abs"]
 
 
 @pytest.mark.parametrize("name", ["attn_short_smooth.npz", "attn_per_head_d64.npz", "attn_mixed_long.npz"])

@@ -102,6 +102,43 @@ int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_
                               size_t workspace_bytes, kvq_stream_t stream);
 
 /*
+ * kvq_int8_decode_attention with a finer q quantization: one dynamic q scale per `q_group` channels instead of one
+ * per (token, head) row. q_group = 32 computes the reference's q_gran="group32" numerics (kvq/int8_ref.py:120-130;
+ * CONFIGS["B_channel_smooth_qgroup32"], :220): the integer dot product of every 32-channel slice is scaled by the
+ * slice's own q scale and the slices are summed in fp32. q_group = 0 or head_dim is kvq_int8_decode_attention itself.
+ * Everything else (arguments, workspace, skipped requests, P quantization, output) is unchanged. The reference's CUDA
+ * kernel has no such mode (its group-32 scales exist only in the standalone quant_q and in the PyTorch
+ * implementation); this entry point brings that accuracy option to the INT8 tensor-core path.
+ */
+int kvq_int8_decode_attention_qgroup(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int32_t* cu_q, const int32_t* seq_lens, const int32_t* block_table,
+                                     const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+                                     int num_q_heads, int num_kv_heads, int head_dim, int block_size,
+                                     int64_t num_blocks, int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t,
+                                     int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
+                                     int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+                                     int k_per_channel, int v_per_channel, int max_query_len, int qmax, int q_group,
+                                     void* workspace, size_t workspace_bytes, kvq_stream_t stream);
+
+/*
+ * Prefill / decode disaggregation: the raw int8 pages of a request as one contiguous buffer, and back. The reference
+ * moves its int8_static pages between a prefill and a decode instance byte for byte through vLLM's KV connector and
+ * never sends the static scales, which both sides load from the same file (docs/LOG.md:614-633: 26.5 KB per token
+ * for 28 layers instead of 53 KB in bf16). kvq_pages_to_wire gathers cache pages page_ids[0 .. num_pages) of one
+ * layer into wire[num_pages][2][block_size][num_kv_heads][head_dim] (K then V of each page, int8);
+ * kvq_wire_to_pages scatters such a buffer into the pages page_ids[] of the receiving cache, which may use other page
+ * ids and another cache layout (strides). 2 * num_kv_heads * head_dim bytes per token and layer cross the wire.
+ */
+int kvq_pages_to_wire(const void* k_cache, const void* v_cache, void* wire, const int32_t* page_ids, int64_t num_pages,
+                      int num_kv_heads, int head_dim, int block_size, int64_t kc_stride_b, int64_t kc_stride_n,
+                      int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h,
+                      kvq_stream_t stream);
+int kvq_wire_to_pages(const void* wire, void* k_cache, void* v_cache, const int32_t* page_ids, int64_t num_pages,
+                      int num_kv_heads, int head_dim, int block_size, int64_t kc_stride_b, int64_t kc_stride_n,
+                      int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h,
+                      kvq_stream_t stream);
+
+/*
  * Debug helper: copy the status word the attention kernels keep in `workspace` to the host (synchronizes
  * `stream`). 0 = clean; non-zero = a bounded wait inside a kernel expired. No reference counterpart.
  */

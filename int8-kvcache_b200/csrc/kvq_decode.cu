@@ -215,7 +215,10 @@ struct Geom {
 // s_chi / s_clo. Called by a full warp. The reference's implementation B does this in double (exact products
 // q * s_k, scale = max / 127, division). FP64 issue is slow on this part, so the same values are carried as
 // unevaluated fp32 pairs (~2^-46); only exact rounding ties take the literal double route.
-template <int D>
+//
+// QG: one q scale per 32 channels instead of one per row (the reference's q_gran="group32", kvq/int8_ref.py:120-130):
+// the maximum is taken over the 8 lanes of a slice, and the slice's score scale (fp32) goes to s_chi[row * D / 32 + slice].
+template <int D, bool QG = false>
 __device__ __forceinline__ void q_quantize_row(const DecodeArgs& a, uint2 raw, const float (&sk)[4], int8_t* s_q,
                                                float* s_chi, float* s_clo, int kvh, int row, int lane) {
   constexpr int QROW = D, LANES = D / 4;
@@ -230,7 +233,7 @@ __device__ __forceinline__ void q_quantize_row(const DecodeArgs& a, uint2 raw, c
     amax = ff_max(amax, ff{fabsf(p.hi), p.hi < 0.f ? -p.lo : p.lo});
   }
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1)
+  for (int o = 1; o < (QG ? 8 : 32); o <<= 1)
     amax = ff_max(amax, ff{__shfl_xor_sync(0xffffffffu, amax.hi, o), __shfl_xor_sync(0xffffffffu, amax.lo, o)});
   // sq = max(amax / 127, 1e-8)
   ff sq;
@@ -257,13 +260,17 @@ __device__ __forceinline__ void q_quantize_row(const DecodeArgs& a, uint2 raw, c
     b[e] = max(-127, min(127, r));
   }
   if (lane_on) *reinterpret_cast<uint32_t*>(&s_q[row * QROW + d0]) = pack4(b[0], b[1], b[2], b[3]);
-  if (lane == 0) {
+  if (QG ? ((lane & 7) == 0 && lane_on) : lane == 0) {
     // score = int32 dot * c, c = s_q [* s_k per head] * softmax_scale kept as an unevaluated hi + lo pair
     ff c = sq;
     if (!a.pc_k) c = ff_mul(c, ff{__ldg(a.ks + kvh), 0.f});
     c = ff_mul(c, ff{a.sm_hi, a.sm_lo});
-    s_chi[row] = c.hi;
-    s_clo[row] = c.lo;
+    if (QG) {
+      s_chi[row * (D / 32) + (lane >> 3)] = c.hi;   // per-slice scores are summed in fp32: the low part is not carried
+    } else {
+      s_chi[row] = c.hi;
+      s_clo[row] = c.lo;
+    }
   }
 }
 
@@ -288,7 +295,7 @@ __device__ __forceinline__ void q_load_scale(const DecodeArgs& a, int kvh, int l
 // q fold + quantize for the rows of m tile `mt` of (request, kv head): one warp per row in a rolled loop (this code
 // runs once per item; kept small because straight-line code that is executed once mostly waits on instruction
 // fetch). The next row's q is loaded while the current one is processed.
-template <int D, int NROWS>
+template <int D, int NROWS, bool QG = false>
 __device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, float* s_chi, float* s_clo, int tok,
                                            int qlen, int kvh, int mt, int warp, int lane) {
   float sk[4];
@@ -297,7 +304,7 @@ __device__ __forceinline__ void q_prologue(const DecodeArgs& a, int8_t* s_q, flo
 #pragma unroll 1
   for (int row = warp; row < NROWS; row += NWARPS) {
     const uint2 nxt = q_load_row<D, NROWS>(a, tok, qlen, kvh, mt, row + NWARPS, lane);
-    q_quantize_row<D>(a, cur, sk, s_q, s_chi, s_clo, kvh, row, lane);
+    q_quantize_row<D, QG>(a, cur, sk, s_q, s_chi, s_clo, kvh, row, lane);
     cur = nxt;
   }
 }
@@ -338,34 +345,19 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
 // like the reference's float(double(dot) * c). Plain fp32 would round c first and then the product; at |score| ~ 100
 // that moves P = exp(score - max) by 1e-5 and flips its int8 quantization far more often than the reference's own
 // noise. nhi = -hi (packed pair).
-//
-// MAGIC (the 16-row variant): the int32 accumulators of the mma start at the bit pattern of 1.5 * 2^23 instead of zero, so
-// the accumulated integer read as a float is 12582912 + dot exactly (|dot| < 2^22: at most 128 x 127 x 127), and one packed
-// subtraction per pair replaces two int -> float conversions. The 8-row decode variant keeps the conversions: it runs at the
-// pace of the memory system and its instruction stream is left as it is.
-constexpr int MAGIC_BITS = 0x4B400000;
-constexpr float MAGIC_F = 12582912.f;
-template <bool MAGIC>
-__device__ __forceinline__ f32x2 ints_to_f32x2(int d0, int d1) {
-  if (MAGIC) {
-    f32x2 r;
-    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(pk2(__int_as_float(d0), __int_as_float(d1))), "l"(pk2(MAGIC_F, MAGIC_F)));
-    return r;
-  }
-  return pk2(static_cast<float>(d0), static_cast<float>(d1));
-}
-template <bool MAGIC>
+__device__ __forceinline__ f32x2 ints_to_f32x2(int d0, int d1) { return pk2(static_cast<float>(d0), static_cast<float>(d1)); }
 __device__ __forceinline__ void score2(int d0, int d1, f32x2 hi, f32x2 nhi, f32x2 lo, float& s0, float& s1) {
-  const f32x2 d = ints_to_f32x2<MAGIC>(d0, d1);
+  const f32x2 d = ints_to_f32x2(d0, d1);
   const f32x2 pn = mul2(d, nhi);                       // -(d * hi), rounded
   upk2(sub2(fma2(d, lo, fma2(d, hi, pn)), pn), s0, s1);   // p + (d * lo + (d * hi - p))
 }
 
 // Per-warp state of one m tile: q fragments, score scales, causal limits, running softmax statistics, output.
-template <int D, bool ROWS16>
+template <int D, bool ROWS16, bool QG = false>
 struct TileState {
   uint32_t qa[D / 32][4];
-  float ch0, cl0, ch1, cl1;
+  float ch0, cl0, ch1, cl1;            // one score scale per row (hi + lo)
+  float cg0[QG ? D / 32 : 1], cg1[QG ? D / 32 : 1];   // QG: one score scale per (row, 32-channel slice)
   int lim0, lim1;
   float m0, m1, l0, l1;
   float acc[D / 8][ROWS16 ? 4 : 2];
@@ -373,33 +365,61 @@ struct TileState {
 
 // One 32-key chunk: S = Q.K^T, online softmax, P -> int8, O += P.V. sk / sv: shared-memory addresses of the
 // swizzled K and V tiles; n_base: absolute position of the chunk's first key.
-template <int D, bool ROWS16>
-__device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk, uint32_t sv, int n_base, int lim_all,
+template <int D, bool ROWS16, bool QG>
+__device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t sk, uint32_t sv, int n_base, int lim_all,
                                            int krow, int kmat, int vrow, int t, int hs, int hsel) {
   constexpr int KSTEPS = D / 32, NT = D / 8;
-  // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
-  int sacc[4][4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = ROWS16 ? MAGIC_BITS : 0;
-#pragma unroll
-    for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
-      uint32_t b[4];
-      ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
-      mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
-      mma_s8(sacc[j], s.qa[2 * s2 + 1], b[2], b[3]);
-    }
-  }
   // accumulator (j, e) of lane (g, t): row g (e < 2) or g + 8, key n_base + 8j + 2t + (e & 1)
   const bool need_mask = n_base + CHUNK > lim_all;
   float p0[8], p1[8];
   float mx0 = -INFINITY, mx1 = -INFINITY;
+  if constexpr (QG) {
+    // S = Q.K^T with one q scale per 32-channel slice: every k step of the mma is one slice; its integer dot is scaled
+    // by the slice's scale and the slices are summed in fp32
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      f32x2 a0 = pk2(0.f, 0.f), a1 = pk2(0.f, 0.f);
+#pragma unroll
+      for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
+        uint32_t b[4];
+        ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          int d[4];
+          d[0] = d[1] = d[2] = d[3] = 0;
+          mma_s8(d, s.qa[2 * s2 + h], b[2 * h], b[2 * h + 1]);
+          const float c0 = s.cg0[2 * s2 + h], c1 = s.cg1[2 * s2 + h];
+          a0 = fma2(ints_to_f32x2(d[0], d[1]), pk2(c0, c0), a0);
+          if (ROWS16) a1 = fma2(ints_to_f32x2(d[2], d[3]), pk2(c1, c1), a1);
+        }
+      }
+      upk2(a0, p0[2 * j], p0[2 * j + 1]);
+      if (ROWS16) upk2(a1, p1[2 * j], p1[2 * j + 1]);
+    }
+  }
+  // S = Q.K^T: 4 n-tiles of 8 keys, natural key order
+  int sacc[4][4];
+  if constexpr (!QG) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
+#pragma unroll
+      for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
+        uint32_t b[4];
+        ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
+        mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
+        mma_s8(sacc[j], s.qa[2 * s2 + 1], b[2], b[3]);
+      }
+    }
+  }
   const f32x2 hi0 = pk2(s.ch0, s.ch0), nhi0 = pk2(-s.ch0, -s.ch0), lo0 = pk2(s.cl0, s.cl0);
   const f32x2 hi1 = pk2(s.ch1, s.ch1), nhi1 = pk2(-s.ch1, -s.ch1), lo1 = pk2(s.cl1, s.cl1);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    score2<ROWS16>(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
-    if (ROWS16) score2<ROWS16>(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
+    if constexpr (!QG) {
+      score2(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
+      if (ROWS16) score2(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
+    }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int n = n_base + 8 * j + 2 * t + e;
@@ -468,18 +488,19 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16>& s, uint32_t sk,
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
       int pacc[4];
-      pacc[0] = pacc[1] = pacc[2] = pacc[3] = ROWS16 ? MAGIC_BITS : 0;
+      pacc[0] = pacc[1] = pacc[2] = pacc[3] = 0;
       mma_s8(pacc, pa, b[h2], b[2 + h2]);
       float* o = s.acc[2 * jp + h2];
       // (o0, o1) = (x0, x1) * ps + (o0, o1) * al
-      upk2(fma2(ints_to_f32x2<ROWS16>(pacc[0], pacc[1]), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
+      upk2(fma2(ints_to_f32x2(pacc[0], pacc[1]), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
       if (ROWS16)
-        upk2(fma2(ints_to_f32x2<ROWS16>(pacc[2], pacc[3]), ps1_2, mul2(pk2(o[2], o[3]), al1_2)), o[2], o[3]);
+        upk2(fma2(ints_to_f32x2(pacc[2], pacc[3]), ps1_2, mul2(pk2(o[2], o[3]), al1_2)), o[2], o[3]);
     }
   }
 }
 
-template <int D, bool ROWS16>
+// QG: one q scale per 32 channels (kvq_int8_decode_attention_qgroup); otherwise one per row.
+template <int D, bool ROWS16, bool QG>
 __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
     decode_kernel(const DecodeArgs a, const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v) {
   using Gm = Geom<D, ROWS16>;
@@ -691,17 +712,17 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
       if (early_q) {
 #pragma unroll
         for (int k = 0; k < NROWS / NWARPS; ++k)
-          q_quantize_row<D>(a, q_early[k], sk_early, s_q, s_chi, s_clo, kvh, warp + NWARPS * k, lane);
+          q_quantize_row<D, QG>(a, q_early[k], sk_early, s_q, s_chi, s_clo, kvh, warp + NWARPS * k, lane);
       } else {
         for (int sl = 0; sl < GS; ++sl) {   // slot = m tile of the group, or kv head of the head group
           const int mts = a.hg ? 0 : mg * GS + sl;
           if (mts < rs.mtiles)
-            q_prologue<D, NROWS>(a, s_q + sl * 16 * QROW, s_chi + sl * 16, s_clo + sl * 16, tok, qlen,
-                                 kv_base + (a.hg ? sl : 0), mts, warp, lane);
+            q_prologue<D, NROWS, QG>(a, s_q + sl * 16 * QROW, s_chi + sl * 16 * (QG ? KSTEPS : 1), s_clo + sl * 16, tok, qlen,
+                                     kv_base + (a.hg ? sl : 0), mts, warp, lane);
         }
       }
       __syncthreads();
-      TileState<D, ROWS16> ts;
+      TileState<D, ROWS16, QG> ts;
       {
         const int8_t* q_t = s_q + msl * 16 * QROW;
 #pragma unroll
@@ -711,8 +732,20 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
           ts.qa[s][1] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&q_t[(g + 8) * QROW + 32 * s + 4 * t]) : 0u;
           ts.qa[s][3] = ROWS16 ? *reinterpret_cast<const uint32_t*>(&q_t[(g + 8) * QROW + 32 * s + 16 + 4 * t]) : 0u;
         }
-        ts.ch0 = s_chi[msl * 16 + g], ts.cl0 = s_clo[msl * 16 + g];
-        ts.ch1 = s_chi[msl * 16 + g + 8], ts.cl1 = s_clo[msl * 16 + g + 8];
+        if constexpr (QG) {
+          // [slot][16 rows][slices] floats from s_chi on: with four slots this reaches into s_clo, s_m and s_l, which
+          // nobody else uses between the prologue and the barrier below
+          ts.ch0 = ts.cl0 = ts.ch1 = ts.cl1 = 0.f;
+#pragma unroll
+          for (int c = 0; c < KSTEPS; ++c) {
+            ts.cg0[c] = s_chi[(msl * 16 + g) * KSTEPS + c];
+            ts.cg1[c] = s_chi[(msl * 16 + g + 8) * KSTEPS + c];
+          }
+          __syncthreads();   // every warp holds its scales before a warp without chunks writes s_m / s_l at the item's end
+        } else {
+          ts.ch0 = s_chi[msl * 16 + g], ts.cl0 = s_clo[msl * 16 + g];
+          ts.ch1 = s_chi[msl * 16 + g + 8], ts.cl1 = s_clo[msl * 16 + g + 8];
+        }
         // causal key limit per row: key n is visible iff n < L - qlen + 1 + (query token of the row)
         auto row_lim = [&](int r) {
           const int rt = (mtw * 16 + r) / a.G;
@@ -738,7 +771,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
         if (!ok) break;
         if (active) {
           const uint32_t sk = gring + st * SB;
-          chunk_step<D, ROWS16>(ts, sk, sk + SB / 2, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t, HS,
+          chunk_step<D, ROWS16, QG>(ts, sk, sk + SB / 2, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t, HS,
                                 a.hg ? msl : 0);
         }
         __syncwarp();  // every lane is done with this stage before it is refilled
@@ -969,7 +1002,7 @@ using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, voi
 struct DeviceInfo {
   bool ready = false;
   int sms = 0;
-  int occ[2][2] = {{0, 0}, {0, 0}};  // [D == 128][ROWS16] resident CTAs per SM
+  int occ[2][2] = {{0, 0}, {0, 0}};  // [D == 128][ROWS16] resident CTAs per SM (the same with and without QG)
 };
 
 std::mutex g_mu;
@@ -994,8 +1027,12 @@ std::vector<MapEntry> g_maps;
 
 template <int D, bool R16>
 int prepare_variant(int& occ) {
-  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D, R16>::SMEM));
-  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel<D, R16>, NTHREADS, Geom<D, R16>::SMEM));
+  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D, R16>::SMEM));
+  KVQ_CUDA(cudaFuncSetAttribute(decode_kernel<D, R16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Geom<D, R16>::SMEM));
+  int occ_qg = 0;
+  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_kernel<D, R16, false>, NTHREADS, Geom<D, R16>::SMEM));
+  KVQ_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_qg, decode_kernel<D, R16, true>, NTHREADS, Geom<D, R16>::SMEM));
+  occ = std::min(occ, occ_qg);
   occ = std::max(1, std::min(occ, MAX_CTAS_PER_SM));
   return KVQ_OK;
 }
@@ -1141,15 +1178,17 @@ extern "C" __attribute__((visibility("default"))) int kvq_decode_status(const vo
   return KVQ_OK;
 }
 
-extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                         const int32_t* cu_q, const int32_t* seq_lens, const int32_t* block_table,
-                                         const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
-                                         int num_q_heads, int num_kv_heads, int head_dim, int block_size,
-                                         int64_t num_blocks, int64_t q_stride_t, int64_t q_stride_h, int64_t o_stride_t,
-                                         int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
-                                         int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
-                                         int k_per_channel, int v_per_channel, int max_query_len, int qmax,
-                                         void* workspace, size_t workspace_bytes, kvq_stream_t stream) {
+// q_group: channels per q scale. 0 or head_dim: one scale per (query token, q head) row, the reference kernel's numerics;
+// 32: one per 32-channel slice (the reference's q_gran="group32").
+static int decode_attention_impl(const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q,
+                                 const int32_t* seq_lens, const int32_t* block_table, const float* k_scale,
+                                 const float* v_scale, double softmax_scale, int num_seqs, int num_q_heads, int num_kv_heads,
+                                 int head_dim, int block_size, int64_t num_blocks, int64_t q_stride_t, int64_t q_stride_h,
+                                 int64_t o_stride_t, int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n,
+                                 int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h,
+                                 int64_t bt_stride, int k_per_channel, int v_per_channel, int max_query_len, int qmax,
+                                 int q_group, void* workspace, size_t workspace_bytes, kvq_stream_t stream) {
+  KVQ_REQUIRE(q_group == 0 || q_group == head_dim || q_group == 32, "q_group must be 0, head_dim or 32, got %d", q_group);
   KVQ_REQUIRE(head_dim == 64 || head_dim == 128, "head_dim must be 64 or 128, got %d", head_dim);
   KVQ_REQUIRE(block_size >= 16 && (block_size & (block_size - 1)) == 0, "block_size must be a power of two >= 16");
   KVQ_REQUIRE(num_kv_heads > 0 && num_q_heads > 0 && num_q_heads % num_kv_heads == 0, "bad head counts %d/%d",
@@ -1230,23 +1269,60 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
     plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, grid, a.hdr,
                                   reinterpret_cast<int32_t*>(ws + wl.prefix));
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
+  const bool qg = q_group == 32;
+  const dim3 mgrid(std::max(grid - 1, 1), 16 / MERGE_ROWS);
+#define KVQ_LAUNCH_DECODE(DD, R16, QGG) \
+  KVQ_CUDA(launch_pdl(decode_kernel<DD, R16, QGG>, dim3(grid), dim3(NTHREADS), Geom<DD, R16>::SMEM, s, a, tm_k, tm_v))
   if (head_dim == 128) {
-    if (rows16)
-      KVQ_CUDA(launch_pdl(decode_kernel<128, true>, dim3(grid), dim3(NTHREADS), Geom<128, true>::SMEM, s, a, tm_k, tm_v));
-    else
-      KVQ_CUDA(launch_pdl(decode_kernel<128, false>, dim3(grid), dim3(NTHREADS), Geom<128, false>::SMEM, s, a, tm_k, tm_v));
+    if (rows16) {
+      if (qg) KVQ_LAUNCH_DECODE(128, true, true); else KVQ_LAUNCH_DECODE(128, true, false);
+    } else {
+      if (qg) KVQ_LAUNCH_DECODE(128, false, true); else KVQ_LAUNCH_DECODE(128, false, false);
+    }
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    KVQ_CUDA(launch_pdl(merge_kernel<128>, dim3(std::max(grid - 1, 1), 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    KVQ_CUDA(launch_pdl(merge_kernel<128>, mgrid, dim3(MERGE_THREADS), 0, s, a));
   } else {
-    if (rows16)
-      KVQ_CUDA(launch_pdl(decode_kernel<64, true>, dim3(grid), dim3(NTHREADS), Geom<64, true>::SMEM, s, a, tm_k, tm_v));
-    else
-      KVQ_CUDA(launch_pdl(decode_kernel<64, false>, dim3(grid), dim3(NTHREADS), Geom<64, false>::SMEM, s, a, tm_k, tm_v));
+    if (rows16) {
+      if (qg) KVQ_LAUNCH_DECODE(64, true, true); else KVQ_LAUNCH_DECODE(64, true, false);
+    } else {
+      if (qg) KVQ_LAUNCH_DECODE(64, false, true); else KVQ_LAUNCH_DECODE(64, false, false);
+    }
     if (g_ev_stop) KVQ_CUDA(cudaEventRecord(g_ev_stop, s));
-    KVQ_CUDA(launch_pdl(merge_kernel<64>, dim3(std::max(grid - 1, 1), 16 / MERGE_ROWS), dim3(MERGE_THREADS), 0, s, a));
+    KVQ_CUDA(launch_pdl(merge_kernel<64>, mgrid, dim3(MERGE_THREADS), 0, s, a));
   }
+#undef KVQ_LAUNCH_DECODE
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention(
+    const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q, const int32_t* seq_lens,
+    const int32_t* block_table, const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+    int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks, int64_t q_stride_t,
+    int64_t q_stride_h, int64_t o_stride_t, int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n,
+    int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+    int k_per_channel, int v_per_channel, int max_query_len, int qmax, void* workspace, size_t workspace_bytes,
+    kvq_stream_t stream) {
+  return decode_attention_impl(q, k_cache, v_cache, out, cu_q, seq_lens, block_table, k_scale, v_scale, softmax_scale,
+                               num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, q_stride_t, q_stride_h,
+                               o_stride_t, o_stride_h, kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b, vc_stride_n,
+                               vc_stride_h, bt_stride, k_per_channel, v_per_channel, max_query_len, qmax, 0, workspace,
+                               workspace_bytes, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_qgroup(
+    const void* q, const void* k_cache, const void* v_cache, void* out, const int32_t* cu_q, const int32_t* seq_lens,
+    const int32_t* block_table, const float* k_scale, const float* v_scale, double softmax_scale, int num_seqs,
+    int num_q_heads, int num_kv_heads, int head_dim, int block_size, int64_t num_blocks, int64_t q_stride_t,
+    int64_t q_stride_h, int64_t o_stride_t, int64_t o_stride_h, int64_t kc_stride_b, int64_t kc_stride_n,
+    int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, int64_t bt_stride,
+    int k_per_channel, int v_per_channel, int max_query_len, int qmax, int q_group, void* workspace, size_t workspace_bytes,
+    kvq_stream_t stream) {
+  return decode_attention_impl(q, k_cache, v_cache, out, cu_q, seq_lens, block_table, k_scale, v_scale, softmax_scale,
+                               num_seqs, num_q_heads, num_kv_heads, head_dim, block_size, num_blocks, q_stride_t, q_stride_h,
+                               o_stride_t, o_stride_h, kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b, vc_stride_n,
+                               vc_stride_h, bt_stride, k_per_channel, v_per_channel, max_query_len, qmax, q_group, workspace,
+                               workspace_bytes, stream);
 }
 
 extern "C" __attribute__((visibility("default"))) int kvq_debug_kernel_events(void* start_event, void* stop_event) {

@@ -206,6 +206,73 @@ __global__ void __launch_bounds__(kThreads) dequant_pages_kernel(const DequantAr
   }
 }
 
+// ------------------------------------------------------------------------------------------------------
+// Raw int8 pages to and from a contiguous wire buffer (prefill / decode disaggregation). Wire page p holds cache
+// page page_ids[p] as [K | V][block][H][D] bytes; one CTA per page, 16 bytes per item, every load of a thread issued
+// before its first store. Static scales are not part of the transfer: both sides load the same scale file.
+// ------------------------------------------------------------------------------------------------------
+struct WireArgs {
+  int8_t *kc, *vc;          // cache views (read when exporting, written when importing)
+  int8_t* wire;             // [pages][2][block][H][D]
+  const int32_t* page_ids;
+  int H, D, block_size;
+  int64_t kc_sb, kc_sn, kc_sh, vc_sb, vc_sn, vc_sh;
+};
+
+constexpr int kWireItems = 4;
+
+template <bool TO_WIRE>
+__global__ void __launch_bounds__(kThreads) wire_pages_kernel(const WireArgs a) {
+  const int64_t p = blockIdx.x;
+  const int per_row = a.D / 16, per_slot = a.H * per_row, per_side = a.block_size * per_slot;   // 16-byte items
+  const int64_t page = __ldg(a.page_ids + p);
+  int8_t* w = a.wire + p * 2 * per_side * 16;
+  for (int base = threadIdx.x; base < 2 * per_side; base += kThreads * kWireItems) {
+    uint4 v[kWireItems];
+    int8_t* cp[kWireItems];
+#pragma unroll
+    for (int u = 0; u < kWireItems; ++u) {
+      const int i = base + u * kThreads;
+      cp[u] = nullptr;
+      if (i < 2 * per_side) {
+        const int side = i >= per_side, j = i - side * per_side;
+        const int n = j / per_slot, rem = j - n * per_slot, h = rem / per_row, c = (rem - h * per_row) * 16;
+        cp[u] = side ? a.vc + page * a.vc_sb + n * a.vc_sn + h * a.vc_sh + c : a.kc + page * a.kc_sb + n * a.kc_sn + h * a.kc_sh + c;
+        v[u] = TO_WIRE ? ld_stream16(cp[u]) : ld_stream16(w + static_cast<int64_t>(i) * 16);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kWireItems; ++u) {
+      const int i = base + u * kThreads;
+      if (cp[u]) *reinterpret_cast<uint4*>(TO_WIRE ? w + static_cast<int64_t>(i) * 16 : cp[u]) = v[u];
+    }
+  }
+}
+
+int wire_pages(bool to_wire, void* k_cache, void* v_cache, void* wire, const int32_t* page_ids, int64_t num_pages,
+               int num_kv_heads, int head_dim, int block_size, int64_t kc_stride_b, int64_t kc_stride_n, int64_t kc_stride_h,
+               int64_t vc_stride_b, int64_t vc_stride_n, int64_t vc_stride_h, kvq_stream_t stream) {
+  KVQ_REQUIRE(head_dim > 0 && head_dim % 16 == 0, "wire pages: head_dim must be a multiple of 16, got %d", head_dim);
+  KVQ_REQUIRE(num_kv_heads > 0 && block_size > 0, "wire pages: bad sizes");
+  if (num_pages <= 0) return KVQ_OK;
+  KVQ_REQUIRE(k_cache && v_cache && wire && page_ids, "wire pages: null pointer");
+  KVQ_REQUIRE(aligned16(k_cache) && aligned16(v_cache) && aligned16(wire) && kc_stride_b % 16 == 0 && kc_stride_n % 16 == 0 &&
+                  kc_stride_h % 16 == 0 && vc_stride_b % 16 == 0 && vc_stride_n % 16 == 0 && vc_stride_h % 16 == 0,
+              "wire pages: rows must be 16-byte aligned");
+  WireArgs a;
+  a.kc = static_cast<int8_t*>(k_cache), a.vc = static_cast<int8_t*>(v_cache), a.wire = static_cast<int8_t*>(wire);
+  a.page_ids = page_ids, a.H = num_kv_heads, a.D = head_dim, a.block_size = block_size;
+  a.kc_sb = kc_stride_b, a.kc_sn = kc_stride_n, a.kc_sh = kc_stride_h;
+  a.vc_sb = vc_stride_b, a.vc_sn = vc_stride_n, a.vc_sh = vc_stride_h;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (to_wire)
+    wire_pages_kernel<true><<<static_cast<unsigned>(num_pages), kThreads, 0, s>>>(a);
+  else
+    wire_pages_kernel<false><<<static_cast<unsigned>(num_pages), kThreads, 0, s>>>(a);
+  KVQ_CUDA(cudaGetLastError());
+  return KVQ_OK;
+}
+
 int ilog2_exact(int x) {
   if (x <= 0 || (x & (x - 1))) return -1;
   int s = 0;
@@ -306,4 +373,20 @@ extern "C" __attribute__((visibility("default"))) int kvq_dequant_pages(const vo
   dequant_pages_kernel<<<static_cast<unsigned>(num_pages), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
   KVQ_CUDA(cudaGetLastError());
   return KVQ_OK;
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_pages_to_wire(const void* k_cache, const void* v_cache, void* wire, const int32_t* page_ids,
+                                 int64_t num_pages, int num_kv_heads, int head_dim, int block_size, int64_t kc_stride_b,
+                                 int64_t kc_stride_n, int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n,
+                                 int64_t vc_stride_h, kvq_stream_t stream) {
+  return wire_pages(true, const_cast<void*>(k_cache), const_cast<void*>(v_cache), wire, page_ids, num_pages, num_kv_heads,
+                    head_dim, block_size, kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b, vc_stride_n, vc_stride_h, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_wire_to_pages(const void* wire, void* k_cache, void* v_cache, const int32_t* page_ids,
+                                 int64_t num_pages, int num_kv_heads, int head_dim, int block_size, int64_t kc_stride_b,
+                                 int64_t kc_stride_n, int64_t kc_stride_h, int64_t vc_stride_b, int64_t vc_stride_n,
+                                 int64_t vc_stride_h, kvq_stream_t stream) {
+  return wire_pages(false, k_cache, v_cache, const_cast<void*>(wire), page_ids, num_pages, num_kv_heads, head_dim, block_size,
+                    kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b, vc_stride_n, vc_stride_h, stream);
 }

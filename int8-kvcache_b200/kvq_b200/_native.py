@@ -20,6 +20,8 @@ SIGNATURES = {
     "kvq_decode_workspace_size": (ctypes.c_size_t, [_c_int, _c_int]),
     "kvq_int8_decode_attention": (_c_int, [_c_ptr] * 9 + [ctypes.c_double] + [_c_int] * 5 + [_c_i64] * 12 +
                                   [_c_int] * 4 + [_c_ptr, ctypes.c_size_t, _c_ptr]),
+    "kvq_int8_decode_attention_qgroup": (_c_int, [_c_ptr] * 9 + [ctypes.c_double] + [_c_int] * 5 + [_c_i64] * 12 +
+                                         [_c_int] * 5 + [_c_ptr, ctypes.c_size_t, _c_ptr]),
     "kvq_static_workspace_bytes": (ctypes.c_size_t, []),
     "kvq_int8_decode_attention_noalloc": (_c_int, [_c_ptr] * 9 + [ctypes.c_double] + [_c_int] * 5 + [_c_i64] * 12 +
                                           [_c_int] * 4 + [_c_ptr]),
@@ -29,6 +31,8 @@ SIGNATURES = {
     "kvq_int8_prefill_attention": (_c_int, [_c_ptr] * 9 + [ctypes.c_double, _c_int, _c_i64] + [_c_int] * 4 + [_c_i64] * 12 +
                                    [_c_int] * 3 + [_c_ptr, ctypes.c_size_t, _c_ptr]),
     "kvq_calib_stats": (_c_int, [_c_ptr] * 3 + [_c_i64, _c_int, _c_int] + [_c_i64] * 4 + [_c_ptr] * 9 + [_c_ptr]),
+    "kvq_pages_to_wire": (_c_int, [_c_ptr] * 4 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 6 + [_c_ptr]),
+    "kvq_wire_to_pages": (_c_int, [_c_ptr] * 4 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 6 + [_c_ptr]),
     "kvq_dequant_pages": (_c_int, [_c_ptr] * 9 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 7 + [_c_int, _c_int, _c_ptr]),
 }
 

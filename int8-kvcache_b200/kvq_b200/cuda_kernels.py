@@ -151,13 +151,19 @@ def decode_workspace(device, num_seqs, head_dim):
     return _WORKSPACES.get(device, need)
 
 
+# Channels per q scale inside the attention kernel: unset / 0 = one scale per (token, head) row, the reference CUDA
+# kernel's numerics; 32 = the reference's q_gran="group32" accuracy option (kvq/int8_ref.py:120-130).
+Q_GROUP = int(os.environ.get("KVQ_Q_GROUP", 0))
+
+
 def decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static,
-                     segm=None, max_query_len=1):
+                     segm=None, max_query_len=1, q_group=None):
     """INT8 attention for the requests with at most SHORT_Q query tokens; others are skipped and their rows of
     `out` left untouched (kvq/cuda_kernels.py:51-58). max_query_len bounds the short queries' length.
 
     `segm` (vLLM's split-KV scratch in the reference) is accepted for signature compatibility and not used:
-    the kernel divides the work over the SMs itself and keeps its partial results in its own workspace."""
+    the kernel divides the work over the SMs itself and keeps its partial results in its own workspace.
+    q_group (default: KVQ_Q_GROUP, normally unset) = 32 quantizes q with one scale per 32 channels."""
     ks, vs = static["k_scale"], static["v_scale"]
     _is_cuda(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, ks, vs)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -178,12 +184,12 @@ def decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_tab
     vc, vc_sb, vc_sn, vc_sh = _cache_args(v_cache)
     pk, pv = _scale_flags(ks, vs)
     ws = decode_workspace(q.device, num_seqs, q.size(2))
-    _native.check(ext().kvq_int8_decode_attention(
+    _native.check(ext().kvq_int8_decode_attention_qgroup(
         q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
         ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(1), k_cache.size(2), q.size(2),
         k_cache.size(1), k_cache.size(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1), kc_sb, kc_sn, kc_sh,
-        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, int(max_query_len), SHORT_Q, ws.data_ptr(), ws.numel(),
-        _stream()))
+        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, int(max_query_len), SHORT_Q,
+        int(Q_GROUP if q_group is None else q_group), ws.data_ptr(), ws.numel(), _stream()))
     return out
 
 
@@ -301,11 +307,16 @@ def long_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table
 _PREFILL_WS = _StreamWorkspaces(lambda n: ext().kvq_prefill_workspace_size(n), (4096,))
 
 
-def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static):
+def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, softmax_scale, static,
+                      min_query_len=None):
     """Causal attention for the requests with more than SHORT_Q query tokens, read straight from the INT8 pages
     (tcgen05 tensor-core kernel; no temporary bf16 cache, no plan). Requests with at most SHORT_Q query tokens are
     skipped and their rows of `out` left untouched. Same result as long_attention up to bf16/fp16 rounding:
-    q against K = k_i8 * k_scale, V = v_i8 * v_scale ("implementation A", kvq/int8_ref.py:62-91)."""
+    q against K = k_i8 * k_scale, V = v_i8 * v_scale ("implementation A", kvq/int8_ref.py:62-91).
+
+    min_query_len (default SHORT_Q) moves the threshold: 0 serves every request, decode included, with
+    implementation A numerics (unquantized q and P; the reference's A_* configurations, kvq/int8_ref.py:201-222). That
+    is an accuracy reference for the INT8 kernel, not a fast path: single-token queries fill 7 of a tile's 128 rows."""
     ks, vs = static["k_scale"], static["v_scale"]
     _is_cuda(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_table, ks, vs)
     if q.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
@@ -330,7 +341,8 @@ def prefill_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_ta
         q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
         ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(0), q.size(1), k_cache.size(2), q.size(2),
         k_cache.size(1), k_cache.size(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1), kc_sb, kc_sn, kc_sh,
-        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, SHORT_Q, ws.data_ptr(), ws.numel(), _stream()))
+        vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, SHORT_Q if min_query_len is None else int(min_query_len),
+        ws.data_ptr(), ws.numel(), _stream()))
     return out
 
 

@@ -44,7 +44,7 @@ def to_dev(static):
     return {k: v.to(DEV) for k, v in static.items()}
 
 
-def run_decode(case, max_query_len=None, out=None, interleaved=False, device_case=None):
+def run_decode(case, max_query_len=None, out=None, interleaved=False, device_case=None, q_group=None):
     """decode_attention on the case's int8 cache; returns the bf16 output as a CPU float32 array.
     interleaved=True stores K and V in one [nb, bs, H, 2D] tensor (vLLM's layout) and passes strided views."""
     q = case["q"].to(DEV)
@@ -56,19 +56,20 @@ def run_decode(case, max_query_len=None, out=None, interleaved=False, device_cas
     out = torch.zeros_like(q) if out is None else out
     mql = max_query_len if max_query_len is not None else max(case["q_lens"])
     ck.decode_attention(q, kq, vq, out, case["cu_seqlens_q"].to(DEV), case["seq_lens"].to(DEV),
-                        case["block_table"].to(DEV), case["softmax_scale"], to_dev(case["static"]), max_query_len=mql)
+                        case["block_table"].to(DEV), case["softmax_scale"], to_dev(case["static"]), max_query_len=mql,
+                        q_group=q_group)
     torch.cuda.synchronize()
     assert ck.decode_status() == 0, "a bounded wait inside the attention kernel expired"
     return out.float().cpu().numpy()
 
 
-def oracle_attention(case, requests=None, short_q=8, long_kv_bf16=True):
+def oracle_attention(case, requests=None, short_q=8, long_kv_bf16=True, q_group=None):
     st = case["static"]
     return orc.paged_static_attention(case["q"].float().numpy(), case["kq"].numpy(), case["vq"].numpy(),
                                       case["cu_seqlens_q"].numpy(), case["seq_lens"].numpy(),
                                       case["block_table"].numpy(), case["softmax_scale"], st["k_scale"].numpy(),
                                       st["v_scale"].numpy(), short_q=short_q, p_tile=32, requests=requests,
-                                      long_kv_bf16=long_kv_bf16)
+                                      long_kv_bf16=long_kv_bf16, q_group=q_group)
 
 
 def short_row_mask(case, limit=8):

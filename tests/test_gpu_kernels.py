@@ -446,3 +446,38 @@ def test_items_follow_each_other_without_draining_the_stream():
     short = short_row_mask(case)
     assert (got[~short] == 7.0).all()
     assert_close(oracle_attention(case)[short], got[short], "stream across items")
+
+
+# ---------------------------------------------------------------------------------------------------
+# one q scale per 32 channels inside the attention kernel (kvq_int8_decode_attention_qgroup)
+# ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["attn_qgroup32.npz", "attn_qgroup32_per_head.npz"])
+def test_group32_q_scales_golden(name):
+    """Against outputs of the reference's own implementation with q_gran="group32" (tests/golden), and the option
+    really changes the result: the per-row kernel does not meet them as closely."""
+    fx = load_golden(name)
+    case = fixture_case(fx)
+    out = run_decode(case, q_group=32)
+    err = assert_close(fx["ref_out"], out, name)
+    per_row = orc.compare(fx["ref_out"], run_decode(case))
+    assert err["rel_l2"] < per_row["rel_l2"]
+
+
+@pytest.mark.parametrize("shape", [(28, 4, 128), (32, 8, 128), (14, 2, 64)])
+@pytest.mark.parametrize("batch", ["decode", "short"])
+@pytest.mark.parametrize("per_channel", [True, False])
+def test_group32_q_scales_match_oracle(shape, batch, per_channel):
+    """Decode (8-row kernel, incl. head pairs at 8 kv heads) and multi-token queries (16-row kernel, warp groups),
+    head_dim 128 and 64, per-channel and per-head K/V scales, smooth-K."""
+    hq, hkv, d = shape
+    q_lens, seq_lens = DECODE if batch == "decode" else SHORT
+    case = workloads.paged_case(300 + hq + d, hq, hkv, d, q_lens, seq_lens, per_channel=per_channel, smooth=True, q_std=3.0)
+    out = run_decode(case, q_group=32)
+    assert_close(oracle_attention(case, q_group=32), out, (shape, batch, per_channel))
+
+
+def test_group32_rejects_other_group_sizes():
+    case = workloads.paged_case(301, 28, 4, 128, [1], [64])
+    with pytest.raises(RuntimeError, match="q_group"):
+        run_decode(case, q_group=16)
+    assert_close(oracle_attention(case), run_decode(case, q_group=128), "q_group = head_dim is the per-row kernel")

@@ -1,16 +1,28 @@
 """A caller of the hot path: one decode step of a Qwen2.5-7B-geometry decoder with an int8_static paged KV cache.
 
-Random-initialised bf16 weights (no checkpoint), plain torch for everything that is not the KV path (embedding,
-RMSNorm, QKV / output / MLP GEMMs through cuBLAS, RoPE, SwiGLU, greedy sampling); per layer the new K/V go through
-`quant_reshape_and_cache` and attention through `decode_attention`. The whole step is captured in one CUDA graph.
+Random-initialised bf16 weights (no checkpoint), library kernels for everything that is not the KV path (embedding,
+fused RMSNorm, QKV / output / MLP GEMMs through cuBLAS with the residual adds in their epilogues, RoPE and SwiGLU
+through vLLM's fused ops where vLLM is importable and plain torch otherwise, greedy sampling); per layer the new K/V go
+through `quant_reshape_and_cache` and attention through `decode_attention`. The whole step is captured in one CUDA graph.
 This is benchmark scaffolding for "decode tokens/s on N GPUs with requests sharded": every rank holds the full
 weights and its own requests and pages; there is no collective inside the step.
 """
 import math
 
 import torch
+import torch.nn.functional as F
 
 from . import cuda_kernels as ck
+
+
+def _library_ops():
+    """vLLM's fused elementwise kernels (in-place rotary embedding, silu-and-mul), or None where vLLM is not there."""
+    try:
+        import vllm._custom_ops as ops   # noqa: F401  (registers torch.ops._C)
+
+        return ops if hasattr(torch.ops, "_C") and hasattr(torch.ops._C, "silu_and_mul") else None
+    except Exception:  # noqa: BLE001
+        return None
 
 QWEN25_7B = dict(layers=28, hidden=3584, hq=28, hkv=4, head_dim=128, mlp=18944, vocab=152064, rope_theta=1e6,
                  rms_eps=1e-6)
@@ -54,6 +66,10 @@ class DecodeStep:
         inv = 1.0 / (g["rope_theta"] ** (torch.arange(0, d, 2, device=device, dtype=torch.float32) / d))
         ang = self.positions.float()[:, None] * inv[None]
         self.cos, self.sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        self.ops = _library_ops()
+        # rotary table for the fused op: row p = [cos(p * inv) | sin(p * inv)]; every request sits at position ctx
+        table = torch.arange(ctx + 1, device=device, dtype=torch.float32)[:, None] * inv[None]
+        self.cos_sin = torch.cat([table.cos(), table.sin()], -1).to(torch.bfloat16)
         self.tokens = torch.randint(0, g["vocab"], (batch,), generator=gen, device=device)
         self.next_tokens = torch.zeros_like(self.tokens)
         self.attn_out = torch.empty(batch, hq, d, dtype=torch.bfloat16, device=device)
@@ -69,8 +85,7 @@ class DecodeStep:
             self.lm_head.numel() * 2
 
     def _rms(self, x, weight):
-        xf = x.float()
-        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.g["rms_eps"])).to(torch.bfloat16) * weight
+        return F.rms_norm(x, (x.shape[-1],), weight, self.g["rms_eps"])
 
     def _rope(self, x):   # x [B, heads, D], rotate-half convention
         d = x.shape[-1]
@@ -83,16 +98,28 @@ class DecodeStep:
         x = self.embed[self.tokens]
         scale = 1.0 / math.sqrt(d)
         for i, l in enumerate(self.layers):
-            qkv = torch.addmm(l["bqkv"], self._rms(x, l["ln1"]), l["wqkv"]).view(self.batch, hq + 2 * hkv, d)
-            q, k, v = self._rope(qkv[:, :hq]), self._rope(qkv[:, hq:hq + hkv]), qkv[:, hq + hkv:]
+            qkv = torch.addmm(l["bqkv"], self._rms(x, l["ln1"]), l["wqkv"])
+            if self.ops is not None:   # rotate q and k in place inside the fused activation
+                self.ops.rotary_embedding(self.positions, qkv[:, :hq * d], qkv[:, hq * d:(hq + hkv) * d], d, self.cos_sin, True)
+                qkv = qkv.view(self.batch, hq + 2 * hkv, d)
+                q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+            else:
+                qkv = qkv.view(self.batch, hq + 2 * hkv, d)
+                qk = self._rope(qkv[:, :hq + hkv])
+                q, k, v = qk[:, :hq], qk[:, hq:], qkv[:, hq + hkv:]
             kc, vc = self.kv[i, 0], self.kv[i, 1]
             ck.quant_reshape_and_cache(k, v, kc, vc, self.slots, l["static"])
             ck.decode_attention(q, kc, vc, self.attn_out, self.cu, self.seq_lens, self.block_table, scale, l["static"])
             if self.trace is not None:
                 self.trace.append(dict(q=q.clone(), k=k.clone(), v=v.clone(), attn_out=self.attn_out.clone()))
-            x = x + self.attn_out.view(self.batch, hq * d) @ l["wo"]
+            x = torch.addmm(x, self.attn_out.view(self.batch, hq * d), l["wo"])
             gu = self._rms(x, l["ln2"]) @ l["wgu"]
-            x = x + (torch.nn.functional.silu(gu[:, :g["mlp"]]) * gu[:, g["mlp"]:]) @ l["wdown"]
+            if self.ops is not None:
+                act = torch.empty(self.batch, g["mlp"], dtype=gu.dtype, device=gu.device)
+                torch.ops._C.silu_and_mul(act, gu)
+            else:
+                act = F.silu(gu[:, :g["mlp"]]) * gu[:, g["mlp"]:]
+            x = torch.addmm(x, act, l["wdown"])
         logits = self._rms(x, self.final_norm) @ self.lm_head
         self.next_tokens.copy_(logits.argmax(-1))
         return self.next_tokens

@@ -374,3 +374,27 @@ def test_calibrate_from_writes_the_six_variants(tmp_path):
     for r in per_rank:
         r["samples"] = {}
     assert len(scales.calibrate_from(per_rank, 4, str(tmp_path / "nosamples"))["variants"]) == 4
+
+
+def test_wire_header_round_trip_and_refusals():
+    """The payload description of the int8 page wire format: geometry and a digest of the layer's scales travel with
+    the pages, and a receiver with another geometry, other scales or an unknown format tag refuses them."""
+    import json
+
+    from kvq_b200 import wire
+
+    static = {"k_scale": torch.rand(4, 128) + 0.01, "v_scale": torch.rand(4, 128) + 0.01, "k_mu": torch.randn(4, 128)}
+    raw = wire.header("model.layers.3.self_attn.attn", num_tokens=100, num_pages=7, block_size=16, num_kv_heads=4,
+                      head_dim=128, static=static)
+    h = wire.check_header(raw, 16, 4, 128, static)
+    assert h["pages"] == 7 and h["tokens"] == 100 and h["bytes"] == 7 * 2 * 16 * 4 * 128 and h["dtype"] == "int8"
+    with pytest.raises(RuntimeError, match="head_dim"):
+        wire.check_header(raw, 16, 4, 64, static)
+    with pytest.raises(RuntimeError, match="other static scales"):
+        wire.check_header(raw, 16, 4, 128, dict(static, k_mu=static["k_mu"] + 1))
+    bad = json.loads(raw)
+    bad["format"] = "something-else/9"
+    with pytest.raises(RuntimeError, match="unknown KV wire format"):
+        wire.check_header(json.dumps(bad).encode(), 16, 4, 128, static)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        wire.export_pages(torch.zeros(2, 16, 4, 128, dtype=torch.int8), torch.zeros(2, 16, 4, 128, dtype=torch.int8), [0])

@@ -20,6 +20,7 @@
 //
 // Numerics follow "implementation B" of the reference (kvq/int8_ref.py:108-143, kernel restatement
 // kvq/cuda/int8_kv.cu:11-15): see include/kvq_b200.h.
+#include <type_traits>
 #include <cuda.h>
 
 #include <mutex>
@@ -85,6 +86,14 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], const uint32_t (&a)[4], uint
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Same with a zero accumulator input: the instruction takes the zero register, so nothing has to be cleared first.
+__device__ __forceinline__ void mma_s8_zero(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
 }
 
 // Unevaluated sum hi + lo of two floats (|lo| <= ulp(hi) / 2): ~48 bits of significand without FP64 instructions.
@@ -365,10 +374,26 @@ struct TileState {
 
 // One 32-key chunk: S = Q.K^T, online softmax, P -> int8, O += P.V. sk / sv: shared-memory addresses of the
 // swizzled K and V tiles; n_base: absolute position of the chunk's first key.
+// The 16-row kernel (multi-token queries) is bound by its instruction stream (ncu: issue slots 56 %, DRAM 18 %), so its
+// step is trimmed where the 8-row step is not (SLIM): mma accumulators start from the zero register instead of being
+// cleared, causal masking is a branch only the last chunks of an item take, and the ldmatrix addresses come from three
+// lane constants (~780 -> ~675 warp instructions per chunk and m tile, config 3 -7 %). The 8-row decode step keeps its
+// instruction sequence on purpose: at large batches its loop runs at the rate HBM serves every SM fairly, and faster
+// variants of it measured slower end to end.
 template <int D, bool ROWS16, bool QG>
 __device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t sk, uint32_t sv, int n_base, int lim_all,
                                            int krow, int kmat, int vrow, int t, int hs, int hsel) {
   constexpr int KSTEPS = D / 32, NT = D / 8;
+  constexpr bool SLIM = ROWS16;
+  // 16-row tiles never run in head-group mode (hs = 1, hsel = 0). There the swizzle bits of a row depend on the lane
+  // alone, tile_off(8 j + krow, c) = 8 j D + tile_off(krow, c) and tile_off(vrow, jp) = tile_off(vrow, 0) ^ (jp << 4):
+  // two K bases and one V base per chunk, the rest are immediate offsets and one XOR per V load.
+  const uint32_t ka0 = sk + tile_off<D>(krow, kmat), ka1 = sk + tile_off<D>(krow, (KSTEPS > 2 ? 4 : 0) + kmat);
+  const uint32_t va = sv + tile_off<D>(vrow, 0);
+  auto k_addr = [&](int j, int s2) {
+    return SLIM ? (s2 ? ka1 : ka0) + j * 8 * D : sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel);
+  };
+  auto v_addr = [&](int jp) { return SLIM ? va ^ (jp << 4) : sv + tile_off<D>(vrow, jp, hs, hsel); };
   // accumulator (j, e) of lane (g, t): row g (e < 2) or g + 8, key n_base + 8j + 2t + (e & 1)
   const bool need_mask = n_base + CHUNK > lim_all;
   float p0[8], p1[8];
@@ -382,7 +407,7 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t
 #pragma unroll
       for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
         uint32_t b[4];
-        ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
+        ldsm_x4(b, k_addr(j, s2));
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           int d[4];
@@ -402,12 +427,15 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t
   if constexpr (!QG) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
+      if (!SLIM) sacc[j][0] = sacc[j][1] = sacc[j][2] = sacc[j][3] = 0;
 #pragma unroll
       for (int s2 = 0; s2 < KSTEPS / 2; ++s2) {
         uint32_t b[4];
-        ldsm_x4(b, sk + tile_off<D>(8 * j + krow, 4 * s2 + kmat, hs, hsel));
-        mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
+        ldsm_x4(b, k_addr(j, s2));
+        if (SLIM && s2 == 0)
+          mma_s8_zero(sacc[j], s.qa[0], b[0], b[1]);
+        else
+          mma_s8(sacc[j], s.qa[2 * s2], b[0], b[1]);
         mma_s8(sacc[j], s.qa[2 * s2 + 1], b[2], b[3]);
       }
     }
@@ -420,15 +448,33 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t
       score2(sacc[j][0], sacc[j][1], hi0, nhi0, lo0, p0[2 * j], p0[2 * j + 1]);
       if (ROWS16) score2(sacc[j][2], sacc[j][3], hi1, nhi1, lo1, p1[2 * j], p1[2 * j + 1]);
     }
+    if (!SLIM) {
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int n = n_base + 8 * j + 2 * t + e;
-      if (need_mask && n >= s.lim0) p0[2 * j + e] = -INFINITY;
-      mx0 = fmaxf(mx0, p0[2 * j + e]);
-      if (ROWS16) {
-        if (need_mask && n >= s.lim1) p1[2 * j + e] = -INFINITY;
-        mx1 = fmaxf(mx1, p1[2 * j + e]);
+      for (int e = 0; e < 2; ++e) {
+        const int n = n_base + 8 * j + 2 * t + e;
+        if (need_mask && n >= s.lim0) p0[2 * j + e] = -INFINITY;
+        mx0 = fmaxf(mx0, p0[2 * j + e]);
+        if (ROWS16) {
+          if (need_mask && n >= s.lim1) p1[2 * j + e] = -INFINITY;
+          mx1 = fmaxf(mx1, p1[2 * j + e]);
+        }
       }
+    }
+  }
+  if (SLIM) {
+    // only an item's last chunks reach a row's causal limit: the masking stays off the common path
+    if (need_mask) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int n = n_base + 8 * (k >> 1) + 2 * t + (k & 1);
+        if (n >= s.lim0) p0[k] = -INFINITY;
+        if (ROWS16 && n >= s.lim1) p1[k] = -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      mx0 = fmaxf(mx0, p0[k]);
+      if (ROWS16) mx1 = fmaxf(mx1, p1[k]);
     }
   }
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
@@ -484,12 +530,16 @@ __device__ __forceinline__ void chunk_step(TileState<D, ROWS16, QG>& s, uint32_t
 #pragma unroll
   for (int jp = 0; jp < NT / 2; ++jp) {
     uint32_t b[4];
-    ldsm_t8_x2(b, sv + tile_off<D>(vrow, jp, hs, hsel));
+    ldsm_t8_x2(b, v_addr(jp));
 #pragma unroll
     for (int h2 = 0; h2 < 2; ++h2) {
       int pacc[4];
-      pacc[0] = pacc[1] = pacc[2] = pacc[3] = 0;
-      mma_s8(pacc, pa, b[h2], b[2 + h2]);
+      if (SLIM) {
+        mma_s8_zero(pacc, pa, b[h2], b[2 + h2]);
+      } else {
+        pacc[0] = pacc[1] = pacc[2] = pacc[3] = 0;
+        mma_s8(pacc, pa, b[h2], b[2 + h2]);
+      }
       float* o = s.acc[2 * jp + h2];
       // (o0, o1) = (x0, x1) * ps + (o0, o1) * al
       upk2(fma2(ints_to_f32x2(pacc[0], pacc[1]), ps0_2, mul2(pk2(o[0], o[1]), al0_2)), o[0], o[1]);
@@ -506,6 +556,9 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
   using Gm = Geom<D, ROWS16>;
   constexpr int KSTEPS = D / 32, NT = D / 8, QROW = Gm::QROW, ACC_RS = Gm::ACC_RS, NSTG = Gm::NSTG, NSTAGE = Gm::NSTAGE;
   constexpr int NROWS = ROWS16 ? 16 : 8;
+  // head groups exist only in single-token decode (the host never sets them for 16-row tiles): a constant there.
+  // (A macro rather than a variable, so that the 8-row kernel keeps reading the launch parameter where it did.)
+#define hgm (ROWS16 ? 0 : a.hg)
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[NSTG];    // TMA landed in the stage
   __shared__ __align__(8) uint64_t s_empty[NSTG];   // every warp of the group is done with the stage
@@ -545,7 +598,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
     const int per = (a.num_seqs + NTHREADS - 1) / NTHREADS;
     const int r0 = tid * per, r1 = min(a.num_seqs, r0 + per);
     auto units_of = [&](int r) {
-      return req_shape(a.cu_q[r + 1] - a.cu_q[r], a.seq_lens[r], a.G, a.Hkv, a.qmax, a.grouped, a.hg).units;
+      return req_shape(a.cu_q[r + 1] - a.cu_q[r], a.seq_lens[r], a.G, a.Hkv, a.qmax, a.grouped, hgm).units;
     };
     int local = 0;
     for (int r = r0; r < r1; ++r) local += units_of(r);
@@ -600,7 +653,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
   int req = s_req, p0 = s_p0;   // the request that owns unit u and its first unit; later requests follow in order
   while (u < uend && req < a.num_seqs) {
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
-    const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, a.hg);
+    const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, hgm);
     if (rs.units == 0) {   // padding (q_len 0) and long requests have no work here
       ++req;
       continue;
@@ -615,9 +668,9 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
               msl = warp & (GS - 1);
     // Ring geometry of a group. m-tile groups: 3 * GS stages of one chunk of one head; head groups: 3 stages of one
     // chunk of GS heads. Either way the group owns 3 * GS * STAGE bytes and keeps PD chunks in flight.
-    const int HS = a.hg ? GS : 1;                                 // heads per TMA box
-    const int RD = a.hg ? NSTAGE : NSTAGE * GS;                   // stages in the ring
-    const int PD = a.hg ? NSTAGE - 1 : (NSTAGE - 1) * GS;         // prefetch distance, in chunks of the group
+    const int HS = hgm ? GS : 1;                                 // heads per TMA box
+    const int RD = hgm ? NSTAGE : NSTAGE * GS;                   // stages in the ring
+    const int PD = hgm ? NSTAGE - 1 : (NSTAGE - 1) * GS;         // prefetch distance, in chunks of the group
     const uint32_t SB = HS * Gm::STAGE;                           // bytes per stage
     if (GS != cur_gs) {
       if (tid == 0) {
@@ -639,15 +692,15 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
     // ---- items (kv head, m-tile group) of this request that intersect [u, uend) ----
     while (u < uend && u < p1) {
       const int item = (u - p0) / nchunks, c0 = (u - p0) - item * nchunks;
-      const int kv_base = a.hg ? item * GS : item / rs.mgroups;       // first (or only) kv head of the item
-      const int mg = a.hg ? 0 : item - kv_base * rs.mgroups;           // m-tile group of the item
-      const int kvh = kv_base + (a.hg ? msl : 0);                      // this warp's kv head
+      const int kv_base = hgm ? item * GS : item / rs.mgroups;       // first (or only) kv head of the item
+      const int mg = hgm ? 0 : item - kv_base * rs.mgroups;           // m-tile group of the item
+      const int kvh = kv_base + (hgm ? msl : 0);                      // this warp's kv head
       const int c1 = min(nchunks, c0 + (uend - u));
       const bool whole = (c0 == 0 && c1 == nchunks);
       // the group consumes chunks c0 + gidx + NG * i, i < nig; inside the group warp msl produces i = msl + GS * ip
       const int nig = (c1 - c0 - gidx + NG - 1) / NG;
       const int npw = (nig - msl + GS - 1) >> lgs;
-      const int mtw = a.hg ? 0 : mg * GS + msl;      // this warp's m tile
+      const int mtw = hgm ? 0 : mg * GS + msl;      // this warp's m tile
       const bool active = mtw < rs.mtiles;
 
       // -- TMA producer: page ids 16 chunks at a time, one lane per 16-key half chunk --
@@ -715,10 +768,10 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
           q_quantize_row<D, QG>(a, q_early[k], sk_early, s_q, s_chi, s_clo, kvh, warp + NWARPS * k, lane);
       } else {
         for (int sl = 0; sl < GS; ++sl) {   // slot = m tile of the group, or kv head of the head group
-          const int mts = a.hg ? 0 : mg * GS + sl;
+          const int mts = hgm ? 0 : mg * GS + sl;
           if (mts < rs.mtiles)
             q_prologue<D, NROWS, QG>(a, s_q + sl * 16 * QROW, s_chi + sl * 16 * (QG ? KSTEPS : 1), s_clo + sl * 16, tok, qlen,
-                                     kv_base + (a.hg ? sl : 0), mts, warp, lane);
+                                     kv_base + (hgm ? sl : 0), mts, warp, lane);
         }
       }
       __syncthreads();
@@ -772,7 +825,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
         if (active) {
           const uint32_t sk = gring + st * SB;
           chunk_step<D, ROWS16, QG>(ts, sk, sk + SB / 2, (c0 + gidx + NG * i) * CHUNK, lim_all, krow, kmat, vrow, t, HS,
-                                a.hg ? msl : 0);
+                                    hgm ? msl : 0);
         }
         __syncwarp();  // every lane is done with this stage before it is refilled
         if (GS > 1 && lane == 0) mbar_arrive(gempty + st * 8);
@@ -814,7 +867,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
       for (int i = tid; i < GS * NROWS * (D / 4); i += NTHREADS) {
         const int sl = i / (NROWS * (D / 4)), rem = i - sl * (NROWS * (D / 4));
         const int row = rem / (D / 4), c4 = (rem - row * (D / 4)) * 4;
-        const int mts = a.hg ? 0 : mg * GS + sl, kvs = kv_base + (a.hg ? sl : 0);   // m tile and kv head of the slot
+        const int mts = hgm ? 0 : mg * GS + sl, kvs = kv_base + (hgm ? sl : 0);   // m tile and kv head of the slot
         const int R = mts * 16 + row, rt = R / a.G, rh = R - rt * a.G;
         if (mts >= rs.mtiles || rt >= qlen) continue;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -869,6 +922,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
 
 // ------------------------------------------------------------------------------------------------------
 // merge of items that were cut across CTAs
+#undef hgm
 // ------------------------------------------------------------------------------------------------------
 constexpr int MERGE_THREADS = 256;
 constexpr int MERGE_ROWS = 2;      // rows of an m tile per block: grid.y = 16 / MERGE_ROWS

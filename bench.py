@@ -354,11 +354,25 @@ def run_ours(args, rank, world, local_rank):
         n = BATCH // world
         q_n, out_n, cu_n, sl_n, bt_n = q[:n], out[:n], cu[:n + 1], sl[:n], bt[:n]
         gathered = torch.empty(BATCH, HQ, D, dtype=out.dtype, device=dev) if world > 1 else None
+        # the gather: this library's peer-store kernel over NVLink where symmetric memory is available, else NCCL
+        peer, collective = None, "none (one GPU)"
+        if world > 1:
+            collective = f"NCCL all_gather of [{n}, {HQ}, {D}] bf16 output rows per rank inside the timed step"
+            try:
+                if os.environ.get("KVQ_GATHER", "peer") == "peer":
+                    peer = sharding.PeerGather(n, (HQ, D), out.dtype, dev)
+                    collective = (f"kvq_peer_allgather: every rank stores its [{n}, {HQ}, {D}] bf16 output rows into every "
+                                  "peer's buffer over NVLink and waits for the peers' flags, inside the timed step")
+            except Exception as e:   # no symmetric memory on this box: the library route
+                collective += f" (peer route unavailable: {type(e).__name__})"
+        out_c = out_n.contiguous()
 
         def strong_step():
-            ck.decode_attention(q_n, kq, vq, out_n, cu_n, sl_n, bt_n, scale, st, max_query_len=1)
-            if world > 1:
-                sharding.gather_outputs(out_n, [n] * world, out=gathered)
+            ck.decode_attention(q_n, kq, vq, out_c, cu_n, sl_n, bt_n, scale, st, max_query_len=1)
+            if peer is not None:
+                peer.gather(out_c)
+            elif world > 1:
+                sharding.gather_outputs(out_c, [n] * world, out=gathered)
 
         for _ in range(3):
             strong_step()
@@ -370,6 +384,8 @@ def run_ours(args, rank, world, local_rank):
         s_stop.record()
         sync_all()
         strong = s_start.elapsed_time(s_stop)
+        if peer is not None:
+            peer.check()   # raises if a wait for a peer's rows ran out
 
     # ---- output check: a seeded subset of the timed batch recomputed by the CPU oracle ----
     check = output_check(case, out_ref=None, ck=ck, rank=rank) if rank == 0 and not args.no_check else None
@@ -417,8 +433,7 @@ def run_ours(args, rank, world, local_rank):
             "workload": f"the fixed {BATCH} x {CTX} layer, {BATCH // world} requests per GPU",
             "us_per_step": s_ms * 1e3, "value": BATCH * CTX * HKV * D * 2 / (s_ms * 1e-3) / 1e9, "unit": UNIT,
             "decode_tok_per_s": BATCH / (s_ms * 1e-3),
-            "collective": ("none (one GPU)" if world == 1 else
-                           f"NCCL all_gather of [{BATCH // world}, {HQ}, {D}] bf16 output rows per rank inside the timed step"),
+            "collective": collective,
             "speedup_vs_one_gpu_step_of_this_run": ms_per_step / s_ms,
             "note": "the weak-scaling step above runs the whole 128-request layer on every GPU, so its time is this "
                     "run's one-GPU time for the fixed layer"}

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB = os.path.join(LIB_DIR, "libkvq_b200.so")
-SOURCES = ["kvq_api.cu", "kvq_quant.cu", "kvq_decode.cu", "kvq_prefill.cu", "kvq_calib.cu"]
+SOURCES = ["kvq_api.cu", "kvq_quant.cu", "kvq_decode.cu", "kvq_prefill.cu", "kvq_calib.cu", "kvq_gather.cu"]
 HEADERS = sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inl"))) + [
     os.path.join(os.path.dirname(HERE), "include", "kvq_b200.h")]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler",

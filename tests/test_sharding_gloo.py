@@ -94,6 +94,48 @@ def test_gather_outputs_nccl(tmp_path):
     assert int(np.load(path)) == 1
 
 
+def _peer_gather_worker(rank, world, port, result_path):
+    torch.cuda.set_device(rank)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world, device_id=dev)
+    ok = True
+    rows, shape = 24, (28, 128)   # 24 x 28 x 128 bf16 = 172 KB per rank: several slices per peer
+    pg = sharding.PeerGather(rows, shape, torch.bfloat16, dev)
+    for step in range(5):         # both buffers, several epochs; every step's rows differ
+        gen = torch.Generator().manual_seed(100 + step)
+        full = torch.randn(world * rows, *shape, generator=gen).to(torch.bfloat16)
+        local = full[rank * rows:(rank + 1) * rows].to(dev).contiguous()
+        got = pg.gather(local)
+        ok = ok and torch.equal(got.cpu(), full)
+        # the NCCL route gives the same rows
+        ok = ok and torch.equal(sharding.gather_outputs(local, [rows] * world).cpu(), full)
+    pg.check()
+    try:
+        pg.gather(local[:1])
+        ok = False
+    except ValueError:
+        pass
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        np.save(result_path, int(flag.item()))
+    dist.barrier()
+    del pg
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_peer_gather_two_gpus(tmp_path):
+    """kvq_peer_allgather between two GPUs of the node: every rank's rows reach both buffers, step after step
+    (skipped on a single-GPU box)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    path = str(tmp_path / "ok.npy")
+    mp.spawn(_peer_gather_worker, args=(2, _free_port(), path), nprocs=2, join=True)
+    assert int(np.load(path)) == 1
+
+
 @pytest.mark.parametrize("interleaved", [False, True])
 def test_sharded_attention_equals_unsharded(tmp_path, interleaved):
     path = str(tmp_path / "diff.npy")

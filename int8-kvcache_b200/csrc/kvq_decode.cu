@@ -20,6 +20,7 @@
 //
 // Numerics follow "implementation B" of the reference (kvq/int8_ref.py:108-143, kernel restatement
 // kvq/cuda/int8_kv.cu:11-15): see include/kvq_b200.h.
+#include <cstdlib>
 #include <type_traits>
 #include <cuda.h>
 
@@ -39,7 +40,7 @@ constexpr int NTHREADS = NWARPS * 32;
 constexpr int FUSED_PLAN_MAX = 1024;  // up to this many requests every CTA sums the work itself; beyond, plan_kernel runs first
 constexpr int MIN_UNITS = 4;   // never give a CTA less than one chunk per warp
 constexpr int MAX_CTAS_PER_SM = 4;
-constexpr int HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total units, [2] units per CTA
+constexpr int HDR_BYTES = 256;  // workspace header: int32 [0] status, [1] total units, [2] cost share per CTA, [3] total cost
 constexpr int PART_ROWS = 16;      // rows of one m tile
 constexpr int PART_ROWS_GROUPED = 64;  // rows of a group of up to four m tiles
 
@@ -49,7 +50,7 @@ struct DecodeArgs {
   const int32_t *cu_q, *seq_lens, *block_table;
   const float *ks, *vs;
   int32_t* hdr;
-  const int32_t* prefix;   // [num_seqs + 1] exclusive prefix of per-request units (only when planned)
+  const int32_t* prefix;   // [2][num_seqs + 1] exclusive prefixes of per-request units and costs (only when planned)
   int32_t* cta_status;     // [grid] 1 where a bounded wait of that CTA expired (folded into hdr[0] by the merge kernel)
   int32_t* bnd;            // [grid][8] what the end of each CTA's range cut (written by decode, read by merge)
   float* part_acc;         // [grid * 2][16][D]  numerator * v_scale of a cut item
@@ -62,6 +63,7 @@ struct DecodeArgs {
   int grouped;             // 1: warps of a CTA share K/V streams across m tiles (multi-token queries)
   int hg;                  // 0, or 2 / 4: decode with warps of a group on ADJACENT KV HEADS of one stream (see req_shape)
   int part_rows;           // rows per partial slot: 16, or 64 in grouped mode
+  int item_cost;           // what starting an item costs a CTA, in units (see work_cost)
   int kpos[3], vpos[3];    // tensor-map coordinate slot (1..3) of the (slot-in-block, head, block) dims
 };
 
@@ -135,7 +137,7 @@ __device__ __forceinline__ uint32_t tile_off(int tau, int c16, int hs = 1, int h
 //              heads are contiguous in a token-major cache, so every TMA box reads hg x head_dim contiguous bytes per
 //              key instead of head_dim) and each of the gs = hg warps takes one head
 struct ReqShape {
-  int nchunks, mtiles, gs, mgroups, units;
+  int nchunks, mtiles, gs, mgroups, units, items;   // units = items * nchunks
 };
 __device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped, int hg) {
   ReqShape r;
@@ -143,52 +145,72 @@ __device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, i
   r.mtiles = (qlen * G + 15) / 16;
   if (hg) {
     r.gs = hg, r.mgroups = 1;
-    r.units = (qlen < 1 || qlen > qmax) ? 0 : r.nchunks * (Hkv / hg);
+    r.items = (qlen < 1 || qlen > qmax) ? 0 : Hkv / hg;
+    r.units = r.items * r.nchunks;
     return r;
   }
   r.gs = grouped ? (r.mtiles >= 3 ? 4 : (r.mtiles == 2 ? 2 : 1)) : 1;
   r.mgroups = (r.mtiles + r.gs - 1) / r.gs;
-  r.units = (qlen < 1 || qlen > qmax) ? 0 : r.nchunks * Hkv * r.mgroups;
+  r.items = (qlen < 1 || qlen > qmax) ? 0 : Hkv * r.mgroups;
+  r.units = r.items * r.nchunks;
   return r;
 }
 
+// The CTAs do not split the units evenly but a cost: one per unit plus `item_cost` per item start. Starting an item in
+// the middle of a CTA's range drains its TMA ring, combines the warps, writes the item out and runs the next q prologue
+// (~5 us, measured), so a CTA whose range crosses an item boundary used to finish that much after the others: at small
+// batches (a few long requests over all SMs) those few CTAs set the kernel's time. In cost space an item is a jump of
+// item_cost followed by its units; ranges are equal in cost, and a range boundary that falls inside a jump snaps to the
+// item's first unit, so short ranges stop crossing item boundaries at all.
+__device__ __forceinline__ int work_cost(const ReqShape& r, int item_cost) { return r.units + item_cost * r.items; }
+// Unit (relative to the request's first) at cost f (relative to the request's first): the inverse of the cost function.
+__device__ __forceinline__ int unit_at_cost(const ReqShape& r, int item_cost, int f) {
+  const int per = r.nchunks + item_cost, item = f / per, o = f - item * per;
+  return item * r.nchunks + max(0, o - item_cost);
+}
+
 // ------------------------------------------------------------------------------------------------------
-// plan: units per request, exclusive prefix sum, units per CTA
+// plan: units and cost per request, exclusive prefix sums, cost share per CTA
 // ------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) plan_kernel(const int32_t* __restrict__ cu_q, const int32_t* __restrict__ seq_lens,
-                                                   int num_seqs, int G, int Hkv, int qmax, int grouped, int hg, int nctas,
-                                                   int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
-  __shared__ int s_warp[8];
-  __shared__ int s_carry;
+                                                   int num_seqs, int G, int Hkv, int qmax, int grouped, int hg, int item_cost,
+                                                   int nctas, int32_t* __restrict__ hdr, int32_t* __restrict__ prefix) {
+  __shared__ unsigned long long s_warp[8];
+  __shared__ unsigned long long s_carry;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int32_t* prefix_f = prefix + num_seqs + 1;
   pdl_launch_dependents();   // the attention kernel may set itself up while the plan is computed
   if (tid == 0) s_carry = 0;
   __syncthreads();
   for (int base = 0; base < num_seqs; base += 256) {
     const int r = base + tid;
-    int u = 0;
-    if (r < num_seqs) u = req_shape(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, grouped, hg).units;
-    int x = u;  // inclusive scan inside the warp
+    unsigned long long u = 0;   // cost in the high word, units in the low word
+    if (r < num_seqs) {
+      const ReqShape rs = req_shape(cu_q[r + 1] - cu_q[r], seq_lens[r], G, Hkv, qmax, grouped, hg);
+      u = (static_cast<unsigned long long>(work_cost(rs, item_cost)) << 32) | static_cast<unsigned>(rs.units);
+    }
+    unsigned long long x = u;  // inclusive scan inside the warp
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      const unsigned long long y = __shfl_up_sync(0xffffffffu, x, o);
       if (lane >= o) x += y;
     }
     if (lane == 31) s_warp[warp] = x;
     __syncthreads();
-    int woff = 0;
+    unsigned long long woff = 0;
     for (int w = 0; w < warp; ++w) woff += s_warp[w];
-    const int carry = s_carry;
-    if (r < num_seqs) prefix[r] = carry + woff + x - u;
+    const unsigned long long carry = s_carry, excl = carry + woff + x - u;
+    if (r < num_seqs) prefix[r] = static_cast<int>(excl & 0xffffffffu), prefix_f[r] = static_cast<int>(excl >> 32);
     __syncthreads();
     if (tid == 255) s_carry = carry + woff + x;
     __syncthreads();
   }
   if (tid == 0) {
-    const int total = s_carry;
-    prefix[num_seqs] = total;
+    const int total = static_cast<int>(s_carry & 0xffffffffu), total_f = static_cast<int>(s_carry >> 32);
+    prefix[num_seqs] = total, prefix_f[num_seqs] = total_f;
     hdr[1] = total;
-    hdr[2] = max((total + nctas - 1) / nctas, MIN_UNITS);
+    hdr[2] = max((total_f + nctas - 1) / nctas, MIN_UNITS);
+    hdr[3] = total_f;
   }
 }
 
@@ -562,7 +584,8 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t s_full[NSTG];    // TMA landed in the stage
   __shared__ __align__(8) uint64_t s_empty[NSTG];   // every warp of the group is done with the stage
-  __shared__ int s_req, s_p0, s_scan[NWARPS];
+  __shared__ int s_req, s_p0, s_f0, s_ubeg, s_uend;
+  __shared__ unsigned long long s_scan[NWARPS];
 
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
@@ -584,59 +607,72 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
   fence_proxy_async();   // ordered before the first TMA issue by the __syncthreads of the request search below
   pdl_wait();            // everything above overlapped the plan kernel; its results are read from here on
   pdl_launch_dependents();
-  // ---- this CTA's slice [ubeg, uend) of the global unit range and the request that owns its first unit ----
-  int total, W;
-  if (a.planned) {   // large batches: plan_kernel left the prefix sums of the per-request units
-    total = a.hdr[1], W = a.hdr[2];
-    const int ub = blockIdx.x * W;
-    if (ub < total)
-      for (int r = tid; r < a.num_seqs; r += NTHREADS)
-        if (a.prefix[r] <= ub && ub < a.prefix[r + 1]) s_req = r, s_p0 = a.prefix[r];
+  // ---- this CTA's slice [ubeg, uend) of the global unit range (equal shares of the cost, see work_cost) and the
+  //      request that owns its first unit ----
+  const int P = a.item_cost;
+  auto shape_of = [&](int r) {
+    return req_shape(a.cu_q[r + 1] - a.cu_q[r], a.seq_lens[r], a.G, a.Hkv, a.qmax, a.grouped, hgm);
+  };
+  if (tid == 0) s_ubeg = 0x7fffffff, s_uend = -1;   // -1: the range ends with the last unit
+  __syncthreads();
+  int total, Wf;
+  if (a.planned) {   // large batches: plan_kernel left the prefix sums of the per-request units and costs
+    total = a.hdr[1], Wf = a.hdr[2];
+    const int total_f = a.hdr[3], fb = blockIdx.x * Wf, fe = fb + Wf;
+    const int32_t* prefix_f = a.prefix + a.num_seqs + 1;
+    if (fb < total_f)
+      for (int r = tid; r < a.num_seqs; r += NTHREADS) {
+        const int f0r = prefix_f[r], f1r = prefix_f[r + 1];
+        if (f0r <= fb && fb < f1r) s_req = r, s_p0 = a.prefix[r], s_f0 = f0r, s_ubeg = a.prefix[r] + unit_at_cost(shape_of(r), P, fb - f0r);
+        if (f0r <= fe && fe < f1r) s_uend = a.prefix[r] + unit_at_cost(shape_of(r), P, fe - f0r);
+      }
   } else {
-    // every CTA sums the units itself: thread t takes a contiguous run of requests, the runs are scanned over the
-    // block, and the thread whose run contains the CTA's first unit walks it again to find the request
+    // every CTA sums units and costs itself: thread t takes a contiguous run of requests, the runs are scanned over the
+    // block, and the threads whose runs contain the two ends of the CTA's cost range walk them again
     const int per = (a.num_seqs + NTHREADS - 1) / NTHREADS;
     const int r0 = tid * per, r1 = min(a.num_seqs, r0 + per);
-    auto units_of = [&](int r) {
-      return req_shape(a.cu_q[r + 1] - a.cu_q[r], a.seq_lens[r], a.G, a.Hkv, a.qmax, a.grouped, hgm).units;
-    };
-    int local = 0;
-    for (int r = r0; r < r1; ++r) local += units_of(r);
-    int x = local;
+    unsigned long long local = 0;   // cost in the high word, units in the low word
+    for (int r = r0; r < r1; ++r) {
+      const ReqShape rs = shape_of(r);
+      local += (static_cast<unsigned long long>(work_cost(rs, P)) << 32) | static_cast<unsigned>(rs.units);
+    }
+    unsigned long long x = local;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      const unsigned long long y = __shfl_up_sync(0xffffffffu, x, o);
       if (lane >= o) x += y;
     }
     if (lane == 31) s_scan[warp] = x;
     __syncthreads();
-    int woff = 0;
-    total = 0;
+    unsigned long long woff = 0, sum = 0;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) {
       if (w < warp) woff += s_scan[w];
-      total += s_scan[w];
+      sum += s_scan[w];
     }
-    W = max((total + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), MIN_UNITS);
-    if (blockIdx.x == 0 && tid == 0) a.hdr[1] = total, a.hdr[2] = W;   // for the merge kernel
-    const int ub = blockIdx.x * W, excl = woff + x - local;
-    if (ub < total && excl <= ub && ub < excl + local) {
-      int p = excl;
+    total = static_cast<int>(sum & 0xffffffffu);
+    const int total_f = static_cast<int>(sum >> 32);
+    Wf = max((total_f + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x), MIN_UNITS);
+    if (blockIdx.x == 0 && tid == 0) a.hdr[1] = total, a.hdr[2] = Wf, a.hdr[3] = total_f;
+    const unsigned long long excl = woff + x - local;
+    const int fb = blockIdx.x * Wf, fe = fb + Wf, ex_f = static_cast<int>(excl >> 32), lf = static_cast<int>(local >> 32);
+    const bool has_b = ex_f <= fb && fb < ex_f + lf, has_e = ex_f <= fe && fe < ex_f + lf;
+    if (has_b || has_e) {
+      int p = static_cast<int>(excl & 0xffffffffu), f = ex_f;
       for (int r = r0; r < r1; ++r) {
-        const int ur = units_of(r);
-        if (ub < p + ur) {
-          s_req = r, s_p0 = p;
-          break;
-        }
-        p += ur;
+        const ReqShape rs = shape_of(r);
+        const int fr = work_cost(rs, P);
+        if (has_b && f <= fb && fb < f + fr) s_req = r, s_p0 = p, s_f0 = f, s_ubeg = p + unit_at_cost(rs, P, fb - f);
+        if (has_e && f <= fe && fe < f + fr) s_uend = p + unit_at_cost(rs, P, fe - f);
+        p += rs.units, f += fr;
       }
     }
   }
-  const int ubeg = blockIdx.x * W, uend = min(total, ubeg + W);
+  __syncthreads();
+  const int ubeg = s_ubeg, uend = s_uend < 0 ? total : s_uend;
   // defaults: nothing is cut at the end of this CTA's range, no wait expired (overwritten below where that changes)
   if (tid == 0) a.bnd[blockIdx.x * 8] = -1, a.cta_status[blockIdx.x] = 0;
   if (ubeg >= uend) return;
-  __syncthreads();
 
   // Lane-constant pieces of the ldmatrix addresses.
   // K (non-transposed, 4 matrices of 8 keys x 16 channels): lane l addresses key (l & 7) of matrix l >> 3.
@@ -650,7 +686,8 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
   bool ok = true;
   int u = ubeg;
   bool first_seg = true;
-  int req = s_req, p0 = s_p0;   // the request that owns unit u and its first unit; later requests follow in order
+  int req = s_req, p0 = s_p0, f0 = s_f0;   // the request that owns unit u, its first unit and the cost before it;
+                                           // later requests follow in order
   while (u < uend && req < a.num_seqs) {
     const int tok = a.cu_q[req], qlen = a.cu_q[req + 1] - tok, L = a.seq_lens[req];
     const ReqShape rs = req_shape(qlen, L, a.G, a.Hkv, a.qmax, a.grouped, hgm);
@@ -679,6 +716,7 @@ __global__ void __launch_bounds__(NTHREADS, (Geom<D, ROWS16>::MIN_CTAS))
     }
     ++req;
     p0 = p1;
+    f0 += work_cost(rs, P);
   }
 }
 
@@ -690,9 +728,9 @@ constexpr int MERGE_THREADS = 256;
 constexpr int MERGE_ROWS = 2;      // rows of an m tile per block: grid.y = 16 / MERGE_ROWS
 constexpr int MERGE_SHALLOW = 8;   // up to this many partials per item: one lane group per row, no block cooperation
 
-// One block per (CTA boundary, MERGE_ROWS rows of an m tile). Boundary b is the unit b * W where decode CTA b - 1
-// stops and CTA b starts; CTA b - 1 left a record saying which item (if any) it cut there as the first boundary
-// inside the item, so an item cut by several boundaries is merged once and blocks of other boundaries exit after
+// One block per (CTA boundary, MERGE_ROWS rows of an m tile). Boundary b is where decode CTA b's range stops and CTA
+// b + 1 starts; CTA b left a record saying which item (if any) it cut there as the first boundary inside the item,
+// which of its two partial slots it used and the last CTA the item reaches, so an item cut by several boundaries is merged once and blocks of other boundaries exit after
 // one load. The grid depends only on the decode grid, not on the batch. Two shapes of work:
 //   shallow (the usual case, an item cut into a few partials): each group of D / 4 lanes owns one (m tile, row)
 //     of the item and sums its partials itself, so the m tiles of a group merge side by side without a block barrier;
@@ -716,13 +754,13 @@ __global__ void __launch_bounds__(MERGE_THREADS) merge_kernel(const DecodeArgs a
   const int4 r0 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8);
   if (r0.x < 0) return;
   const int4 r1 = *reinterpret_cast<const int4*>(a.bnd + blockIdx.x * 8 + 4);
-  const int kvh = r0.y, mg = r0.z, A = r0.w, B = r1.x, tok = r1.y, qlen = r1.z, gs = r1.w >> 8, mtiles = r1.w & 0xff;
-  const int W = a.hdr[2], tid = threadIdx.x;
-  const int c_lo = blockIdx.x, c_hi = (B - 1) / W;
+  const int kvh = r0.y, mg = r0.z, tok = r1.y, qlen = r1.z, gs = (r1.w >> 8) & 0xff, mtiles = r1.w & 0xff;
+  const int tid = threadIdx.x;
+  const int c_lo = blockIdx.x, c_hi = r1.x, lo_slot = (r1.w >> 16) & 1;
   const int lane = tid & 31, warp = tid >> 5, np = c_hi - c_lo + 1;
   const int pg = tid / LPP, l4 = tid - pg * LPP;
-  // CTA c_lo reached this item after finishing earlier ones unless its range starts exactly at A
-  auto slot_of = [&](int c, int row) { return (c * 2 + ((c == c_lo && c_lo * W < A) ? 1 : 0)) * a.part_rows + row; };
+  // CTA c_lo reached this item after finishing earlier ones (second slot) unless its range starts with the item
+  auto slot_of = [&](int c, int row) { return (c * 2 + (c == c_lo ? lo_slot : 0)) * a.part_rows + row; };
   // partial row = slot * 16 + row of the tile; slot = m tile of the group, or kv head of a head group
   auto store = [&](int sl, int r16, float4 t, float den) {
     const int mts = a.hg ? 0 : mg * gs + sl, kvs = kvh + (a.hg ? sl : 0);
@@ -954,7 +992,7 @@ struct WorkspaceLayout {
 WorkspaceLayout workspace_layout(int num_seqs, int D, int max_ctas, int part_rows) {
   WorkspaceLayout w;
   w.prefix = HDR_BYTES;
-  w.bnd = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 4, 256);
+  w.bnd = w.prefix + align_up(static_cast<size_t>(num_seqs + 1) * 8, 256);   // units and costs
   w.status = w.bnd + align_up(static_cast<size_t>(max_ctas) * 32, 256);
   w.part_acc = w.status + align_up(static_cast<size_t>(max_ctas) * 4, 256);
   w.part_ml = w.part_acc + static_cast<size_t>(max_ctas) * 2 * part_rows * D * 4;
@@ -992,6 +1030,21 @@ extern "C" __attribute__((visibility("default"))) int kvq_decode_status(const vo
   KVQ_CUDA(cudaMemcpyAsync(status, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
   KVQ_CUDA(cudaStreamSynchronize(s));
   return KVQ_OK;
+}
+
+// What an item start costs a CTA, in units of its own work (one unit = one 32-key chunk of an item). The drained ring,
+// the combination, the epilogue and the q prologue are ~5 us against ~0.35 us per unit in single-token decode (four
+// streams per CTA), i.e. ~14 units; cutting an item also adds its partial rows and a merge. Measured over batch shapes
+// (1 ... 128 requests x 32768, 128 x 4096, 256 x 1024, config 3): 14 ... 28 are equally good within 1-2 %, larger values
+// lose (idle CTAs, uneven ranges); pairs of heads carry twice the bytes per unit.
+static int item_cost_units(bool rows16, int hg) {
+  static const int forced = [] {
+    const char* e = getenv("KVQ_DECODE_ITEM_COST");   // tuning knob: overrides the built-in figures
+    return e ? atoi(e) : -1;
+  }();
+  if (forced >= 0) return forced;
+  (void)rows16;
+  return hg ? 10 : 20;
 }
 
 // q_group: channels per q scale. 0 or head_dim: one scale per (query token, q head) row, the reference kernel's numerics;
@@ -1072,6 +1125,7 @@ static int decode_attention_impl(const void* q, const void* k_cache, const void*
   a.q_st = q_stride_t, a.q_sh = q_stride_h, a.o_st = o_stride_t, a.o_sh = o_stride_h, a.bt_stride = bt_stride;
   a.pc_k = k_per_channel, a.pc_v = v_per_channel;
   a.grouped = grouped, a.hg = hg, a.part_rows = grouped ? PART_ROWS_GROUPED : PART_ROWS;
+  a.item_cost = item_cost_units(rows16, hg);
   CUtensorMap tm_k, tm_v;
   if ((rc = cache_tensor_map(k_cache, num_blocks, block_size, num_kv_heads, head_dim, kc_stride_b, kc_stride_n,
                              kc_stride_h, hg ? hg : 1, &tm_k, a.kpos)) != KVQ_OK)
@@ -1082,7 +1136,7 @@ static int decode_attention_impl(const void* q, const void* k_cache, const void*
 
   auto s = reinterpret_cast<cudaStream_t>(stream);
   if (a.planned)
-    plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, grid, a.hdr,
+    plan_kernel<<<1, 256, 0, s>>>(cu_q, seq_lens, num_seqs, G, num_kv_heads, qmax, grouped, hg, a.item_cost, grid, a.hdr,
                                   reinterpret_cast<int32_t*>(ws + wl.prefix));
   if (g_ev_start) KVQ_CUDA(cudaEventRecord(g_ev_start, s));
   const bool qg = q_group == 32;

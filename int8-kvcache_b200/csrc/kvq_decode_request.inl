@@ -203,7 +203,8 @@
       __syncthreads();
 
       // -- epilogue: 4 channels per thread and step; s_v applied here --
-      const int slot_base = (blockIdx.x * 2 + (first_seg ? 0 : 1)) * a.part_rows;
+      const int seg_slot = first_seg ? 0 : 1;
+      const int slot_base = (blockIdx.x * 2 + seg_slot) * a.part_rows;
       for (int i = tid; i < GS * NROWS * (D / 4); i += NTHREADS) {
         const int sl = i / (NROWS * (D / 4)), rem = i - sl * (NROWS * (D / 4));
         const int row = rem / (D / 4), c4 = (rem - row * (D / 4)) * 4;
@@ -249,7 +250,9 @@
         int4* rec = reinterpret_cast<int4*>(a.bnd + blockIdx.x * 8);
         if (c1 < nchunks && A >= ubeg) {
           rec[0] = make_int4(req, kv_base, mg, A);
-          rec[1] = make_int4(A + nchunks, tok, qlen, (GS << 8) | rs.mtiles);
+          // the last CTA the item reaches: the one whose cost range holds the item's last unit
+          const int f_last = f0 + item * (nchunks + P) + P + nchunks - 1;
+          rec[1] = make_int4(f_last / Wf, tok, qlen, (seg_slot << 16) | (GS << 8) | rs.mtiles);
         } else {
           rec[0] = make_int4(-1, 0, 0, 0);
         }

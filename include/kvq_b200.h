@@ -183,6 +183,19 @@ int kvq_int8_decode_attention_noalloc(const void* q, const void* k_cache, const 
 int kvq_debug_kernel_events(void* start_event, void* stop_event);
 
 /*
+ * Inspection helper (host only, no GPU work): the split of a batch's work over num_ctas CTAs as
+ * kvq_int8_decode_attention's kernel computes it for itself. A unit is one 32-key chunk of one (request, kv head,
+ * group of m tiles) item, numbered request by request; CTA b processes units [ubeg[b], uend[b]). The ranges are equal
+ * shares of a cost (one per unit plus item_cost per item start; pass item_cost < 0 for the library's figure), and a
+ * share boundary that falls on an item start snaps to it. q_lens / seq_lens: host arrays [num_seqs]; grouped /
+ * head_group: the kernel's modes (0 / 0 for single-token decode with fewer than 8 kv heads). No reference counterpart:
+ * the reference gives every request 16 fixed segments (kvq/cuda/int8_kv.cu:196-198).
+ */
+int kvq_debug_decode_split(const int32_t* q_lens, const int32_t* seq_lens, int num_seqs, int group_size, int num_kv_heads,
+                           int qmax, int grouped, int head_group, int item_cost, int num_ctas, int32_t* ubeg,
+                           int32_t* uend);
+
+/*
  * Dequantize pages of the INT8 cache into a temporary bf16 paged cache for the long-query (prefill) path.
  * Replaces dequant_pages(kc, vc, ko, vo, block_table, src_req, src_j, ks, vs), kvq/cuda/int8_kv.cu:650-672
  * (kernel :511-542). Output page p = bf16(rne(int8 page block_table[src_req[p]][src_j[p]] * scale)), laid out

@@ -139,7 +139,7 @@ __device__ __forceinline__ uint32_t tile_off(int tau, int c16, int hs = 1, int h
 struct ReqShape {
   int nchunks, mtiles, gs, mgroups, units, items;   // units = items * nchunks
 };
-__device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped, int hg) {
+__host__ __device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, int qmax, int grouped, int hg) {
   ReqShape r;
   r.nchunks = max(1, (L + CHUNK - 1) / CHUNK);
   r.mtiles = (qlen * G + 15) / 16;
@@ -162,9 +162,9 @@ __device__ __forceinline__ ReqShape req_shape(int qlen, int L, int G, int Hkv, i
 // batches (a few long requests over all SMs) those few CTAs set the kernel's time. In cost space an item is a jump of
 // item_cost followed by its units; ranges are equal in cost, and a range boundary that falls inside a jump snaps to the
 // item's first unit, so short ranges stop crossing item boundaries at all.
-__device__ __forceinline__ int work_cost(const ReqShape& r, int item_cost) { return r.units + item_cost * r.items; }
+__host__ __device__ __forceinline__ int work_cost(const ReqShape& r, int item_cost) { return r.units + item_cost * r.items; }
 // Unit (relative to the request's first) at cost f (relative to the request's first): the inverse of the cost function.
-__device__ __forceinline__ int unit_at_cost(const ReqShape& r, int item_cost, int f) {
+__host__ __device__ __forceinline__ int unit_at_cost(const ReqShape& r, int item_cost, int f) {
   const int per = r.nchunks + item_cost, item = f / per, o = f - item * per;
   return item * r.nchunks + max(0, o - item_cost);
 }
@@ -1193,6 +1193,40 @@ extern "C" __attribute__((visibility("default"))) int kvq_int8_decode_attention_
                                o_stride_t, o_stride_h, kc_stride_b, kc_stride_n, kc_stride_h, vc_stride_b, vc_stride_n,
                                vc_stride_h, bt_stride, k_per_channel, v_per_channel, max_query_len, qmax, q_group, workspace,
                                workspace_bytes, stream);
+}
+
+extern "C" __attribute__((visibility("default"))) int kvq_debug_decode_split(const int32_t* q_lens, const int32_t* seq_lens,
+                                                                            int num_seqs, int group_size, int num_kv_heads,
+                                                                            int qmax, int grouped, int head_group,
+                                                                            int item_cost, int num_ctas, int32_t* ubeg,
+                                                                            int32_t* uend) {
+  // Host restatement of the split decode_kernel computes for itself (same req_shape / work_cost / unit_at_cost).
+  KVQ_REQUIRE(q_lens && seq_lens && ubeg && uend && num_seqs >= 0 && num_ctas > 0 && group_size > 0 && num_kv_heads > 0,
+              "decode_split: bad argument");
+  if (item_cost < 0) item_cost = item_cost_units(group_size * std::min(std::max(qmax, 1), 8) > 8, head_group);
+  std::vector<ReqShape> shapes(num_seqs);
+  long long total = 0, total_f = 0;
+  for (int r = 0; r < num_seqs; ++r) {
+    shapes[r] = req_shape(q_lens[r], seq_lens[r], group_size, num_kv_heads, qmax, grouped, head_group);
+    total += shapes[r].units, total_f += work_cost(shapes[r], item_cost);
+  }
+  KVQ_REQUIRE(total_f < (1ll << 31), "decode_split: more than 2^31 units");
+  const int wf = std::max(static_cast<int>((total_f + num_ctas - 1) / num_ctas), MIN_UNITS);
+  auto unit_of = [&](long long f) -> int {   // global unit at cost f
+    if (f >= total_f) return static_cast<int>(total);
+    long long p = 0, c = 0;
+    for (int r = 0; r < num_seqs; ++r) {
+      const int fr = work_cost(shapes[r], item_cost);
+      if (f < c + fr) return static_cast<int>(p) + unit_at_cost(shapes[r], item_cost, static_cast<int>(f - c));
+      p += shapes[r].units, c += fr;
+    }
+    return static_cast<int>(total);
+  };
+  for (int b = 0; b < num_ctas; ++b) {
+    ubeg[b] = unit_of(static_cast<long long>(b) * wf);
+    uend[b] = unit_of(static_cast<long long>(b + 1) * wf);
+  }
+  return KVQ_OK;
 }
 
 extern "C" __attribute__((visibility("default"))) int kvq_debug_kernel_events(void* start_event, void* stop_event) {

@@ -27,6 +27,7 @@ SIGNATURES = {
                                           [_c_int] * 4 + [_c_ptr]),
     "kvq_decode_status": (_c_int, [_c_ptr, ctypes.POINTER(_c_int), _c_ptr]),
     "kvq_debug_kernel_events": (_c_int, [_c_ptr, _c_ptr]),
+    "kvq_debug_decode_split": (_c_int, [_c_ptr, _c_ptr] + [_c_int] * 8 + [_c_ptr, _c_ptr]),
     "kvq_prefill_workspace_size": (ctypes.c_size_t, [_c_int]),
     "kvq_int8_prefill_attention": (_c_int, [_c_ptr] * 9 + [ctypes.c_double, _c_int, _c_i64] + [_c_int] * 4 + [_c_i64] * 12 +
                                    [_c_int] * 3 + [_c_ptr, ctypes.c_size_t, _c_ptr]),

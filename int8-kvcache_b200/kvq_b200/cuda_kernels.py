@@ -123,9 +123,14 @@ class _StreamWorkspaces:
         self.size_fn, self.floor_args = size_fn, floor_args
         self.live, self.retired = {}, []
 
-    def get(self, device, need):
+    @staticmethod
+    def _key(device):
+        device = torch.device(device)   # "cuda", "cuda:1" and torch.device objects name the same buffers
         index = device.index if device.index is not None else torch.cuda.current_device()
-        key = (index, torch.cuda.current_stream(device).cuda_stream)
+        return index, torch.cuda.current_stream(device).cuda_stream
+
+    def get(self, device, need):
+        key = self._key(device)
         ws = self.live.get(key)
         if ws is None or ws.numel() < need:
             if ws is not None:
@@ -135,8 +140,7 @@ class _StreamWorkspaces:
         return ws
 
     def peek(self, device):
-        index = device.index if device.index is not None else torch.cuda.current_device()
-        return self.live.get((index, torch.cuda.current_stream(device).cuda_stream))
+        return self.live.get(self._key(device))
 
 
 # sized for a generous batch (4096 requests, ~39 MB) so that it rarely grows

@@ -398,3 +398,72 @@ def test_wire_header_round_trip_and_refusals():
         wire.check_header(json.dumps(bad).encode(), 16, 4, 128, static)
     with pytest.raises(RuntimeError, match="no CPU path"):
         wire.export_pages(torch.zeros(2, 16, 4, 128, dtype=torch.int8), torch.zeros(2, 16, 4, 128, dtype=torch.int8), [0])
+
+
+def _split_reference(q_lens, seq_lens, G, Hkv, qmax, item_cost, nctas):
+    """Pure-Python statement of how the attention kernel divides a single-token-decode batch over its CTAs: an item
+    (request, kv head) is `item_cost` of start-up followed by ceil(L / 32) chunks; CTAs take equal shares of that
+    cost; a share boundary inside a start-up belongs to the item's first chunk."""
+    items = []   # (first global unit, chunks) per item, in order
+    unit = 0
+    for ql, L in zip(q_lens, seq_lens):
+        if ql < 1 or ql > qmax:
+            continue
+        n = max(1, -(-L // 32))
+        for _ in range(Hkv):
+            items.append((unit, n))
+            unit += n
+    total = unit
+    total_f = total + item_cost * len(items)
+    wf = max(-(-total_f // nctas), 4)
+
+    def unit_of(f):
+        if f >= total_f:
+            return total
+        c = 0
+        for first, n in items:
+            if f < c + item_cost + n:
+                return first + max(0, f - c - item_cost)
+            c += item_cost + n
+        return total
+    return [unit_of(b * wf) for b in range(nctas)], [unit_of((b + 1) * wf) for b in range(nctas)], total, items
+
+
+def test_decode_split_is_contiguous_cost_balanced_and_snaps_to_items():
+    """kvq_debug_decode_split (the host restatement of the kernel's own split, same inline functions): the ranges tile
+    the units in order, equal the pure-Python statement, no range costs more than a share, and with an item cost
+    ranges begin at item starts far more often than an even split of the units would."""
+    import ctypes
+
+    from kvq_b200 import _native
+    lib = _native.lib()
+    rng = np.random.default_rng(7)
+    for (b, lo, hi, nctas, cost) in [(1, 32768, 32768, 296, 20), (8, 32768, 32768, 296, 20), (16, 32768, 32768, 296, 14),
+                                     (128, 32768, 32768, 296, 20), (37, 1, 5000, 296, 20), (300, 17, 900, 296, 0),
+                                     (5, 1, 40, 296, 20), (64, 4096, 4096, 148, 28)]:
+        seq = rng.integers(lo, hi + 1, b).astype(np.int32)
+        ql = np.ones(b, dtype=np.int32)
+        if b > 4:
+            ql[3] = 0          # a padded request has no work
+        ub = np.zeros(nctas, dtype=np.int32)
+        ue = np.zeros(nctas, dtype=np.int32)
+        rc = lib.kvq_debug_decode_split(ql.ctypes.data_as(ctypes.c_void_p), seq.ctypes.data_as(ctypes.c_void_p), b, 7, 4, 8,
+                                        0, 0, cost, nctas, ub.ctypes.data_as(ctypes.c_void_p), ue.ctypes.data_as(ctypes.c_void_p))
+        assert rc == 0
+        rb, re_, total, items = _split_reference(ql.tolist(), seq.tolist(), 7, 4, 8, cost, nctas)
+        assert ub.tolist() == rb and ue.tolist() == re_
+        assert ub[0] == 0 and ue[-1] == total and np.all(ub[1:] == ue[:-1]) and np.all(ue >= ub)
+        starts = {first for first, _ in items}
+        share = max(-(-(total + cost * len(items)) // nctas), 4)
+        for lo_u, hi_u in zip(ub.tolist(), ue.tolist()):
+            inside = sum(1 for s in starts if lo_u < s < hi_u)      # item starts strictly inside the range
+            assert (hi_u - lo_u) + cost * inside <= share
+    # snapping: 8 x 32768 over 296 CTAs; ranges that begin exactly at an item start
+    seq = np.full(8, 32768, dtype=np.int32)
+    ql = np.ones(8, dtype=np.int32)
+    snapped = {}
+    for cost in (0, 20):
+        rb, _, _, items = _split_reference(ql.tolist(), seq.tolist(), 7, 4, 8, cost, 296)
+        starts = {first for first, _ in items}
+        snapped[cost] = sum(1 for u in rb if u in starts)
+    assert snapped[20] >= 4 * snapped[0]

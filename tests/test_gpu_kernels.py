@@ -213,6 +213,58 @@ def test_single_long_request_is_split_over_many_ctas():
     assert_close(oracle_attention(case), run_decode(case), "split short-q")
 
 
+def test_kernel_split_equals_host_restatement():
+    """The records the attention kernel leaves for the merge kernel (which item each CTA's range end cut, and the
+    last CTA that item reaches) agree with the host restatement of the split (kvq_debug_decode_split), for decode
+    batches on the fused path and beyond 1024 requests on the planned one."""
+    import ctypes
+
+    lib = ck.ext()
+    sms = torch.cuda.get_device_properties(DEV).multi_processor_count
+    nctas = 2 * sms                                    # the 8-row kernel runs two CTAs per SM
+    for seed, lens in ((61, [32768] * 3), (62, [5000, 20000, 777, 12345, 64]), (63, None)):
+        if lens is None:                               # planned path: more than 1024 requests
+            lens = np.random.default_rng(seed).integers(1, 400, 1200).tolist()
+        b = len(lens)
+        case = workloads.paged_case(seed, 28, 4, 128, [1] * b, lens)
+        run_decode(case)
+        torch.cuda.synchronize()
+        ws = ck.decode_workspace(DEV, b, 128)
+        raw = ws.view(torch.int32).cpu().numpy()
+        bnd0 = (256 + -(-((b + 1) * 8) // 256) * 256) // 4
+        rec = raw[bnd0:bnd0 + nctas * 8].reshape(nctas, 8)
+        ql = np.ones(b, dtype=np.int32)
+        sl = np.asarray(lens, dtype=np.int32)
+        ub = np.zeros(nctas, dtype=np.int32)
+        ue = np.zeros(nctas, dtype=np.int32)
+        assert lib.kvq_debug_decode_split(ql.ctypes.data_as(ctypes.c_void_p), sl.ctypes.data_as(ctypes.c_void_p), b, 7, 4, 8,
+                                          0, 0, -1, nctas, ub.ctypes.data_as(ctypes.c_void_p),
+                                          ue.ctypes.data_as(ctypes.c_void_p)) == 0
+        # items in unit order: (first unit, chunks, request, kv head)
+        items, u = [], 0
+        for r, L in enumerate(lens):
+            n = max(1, -(-L // 32))
+            for h in range(4):
+                items.append((u, n, r, h))
+                u += n
+        firsts = np.asarray([it[0] for it in items])
+        cuts = 0
+        for c in range(nctas - 1):
+            e = int(ue[c])
+            k = int(np.searchsorted(firsts, e, side="right")) - 1
+            first, n, r, h = items[k]
+            cut_here = ub[c] < ue[c] and first < e < first + n and first >= ub[c]   # first boundary inside the item
+            if cut_here:
+                cuts += 1
+                last = first + n - 1
+                last_cta = next(cc for cc in range(nctas) if ub[cc] <= last < ue[cc])
+                assert (rec[c, 0], rec[c, 1], rec[c, 3]) == (r, h, first), (c, rec[c], (r, h, first))
+                assert rec[c, 4] == last_cta, (c, rec[c], last_cta)
+            else:
+                assert rec[c, 0] < 0, (c, rec[c])
+        assert cuts > 0
+
+
 def test_headline_shape_subset_vs_oracle():
     """Full-size contexts (32768) at a batch the oracle finishes in seconds; the decode kernel sees 8 requests."""
     case = workloads.paged_case(35, 28, 4, 128, [1] * 8, [32768] * 8, num_blocks=8 * 2048 + 8)

@@ -87,7 +87,8 @@ size_t kvq_decode_workspace_size(int num_seqs, int head_dim);
  * Numerics ("implementation B"): q' = q * k_scale (per channel), quantized per (token, head); scores from
  * int8 x int8 -> int32 tensor-core products; fp32 online softmax; P quantized to int8 per (row, 32-key tile
  * at absolute positions); P.V in int8 -> int32; denominator from the quantized P; output * v_scale -> bf16.
- * Split-KV is chosen internally (work is divided evenly over the SMs) and merged by a second kernel; both
+ * Split-KV is chosen internally (work is divided over the SMs by the kernel itself, see kvq_debug_decode_split) and
+ * merged by a second kernel; both
  * use `workspace` (>= kvq_decode_workspace_size bytes, 256-byte aligned). Calls that share a workspace must
  * not overlap on the GPU.
  */

@@ -3,12 +3,13 @@
 // Two launches per call (three for batches of more than FUSED_PLAN_MAX requests), all on the caller's stream, no host
 // synchronization:
 //   decode_kernel   one CTA per slice of the global unit range (a unit is one 32-key chunk of one item; the range is
-//                   cut evenly over #SMs x resident CTAs, so every CTA streams the same number of KV bytes whatever
-//                   the mix of context lengths); a slice covers whole (request, kv head, m-tile group) items and at
+//                   cut into equal shares of a cost, one per unit plus a figure per item start, over #SMs x resident
+//                   CTAs, so every CTA streams nearly the same number of KV bytes whatever the mix of context lengths
+//                   and short ranges do not cross item boundaries); a slice covers whole (request, kv head, m-tile group) items and at
 //                   most two partial ones, whose (acc, max, sum) go to the workspace. Every CTA sums the per-request
 //                   work itself to find its slice (a block scan over the requests instead of a kernel boundary)
 //   merge_kernel    items that were cut across CTAs: combine their partials into the output; folds the CTAs' status
-//   plan_kernel     large batches only, first: per-request units and their exclusive prefix sum in the workspace, so
+//   plan_kernel     large batches only, first: per-request units and costs, their exclusive prefix sums in the workspace, so
 //                   that hundreds of CTAs do not each walk thousands of requests
 //
 // Inside decode_kernel the four warps of a CTA form groups of 1, 2 or 4 (per request, by its number of 16-row

@@ -262,7 +262,8 @@ int kvq_calib_stats(const void* key, const void* value, const int64_t* slots, in
  *   status          device int in this rank's memory: set to 1 when a wait for a peer ran out (about a second)
  * The caller alternates between two sets of gather buffers from step to step (a rank may be one step ahead of the
  * slowest one) and orders the consumer of the gathered rows after this call on `stream`. Every rank must make the same
- * sequence of calls. One launch, no host synchronization, capturable.
+ * sequence of calls. One launch, no host synchronization. Not for replay from a CUDA graph: the epoch is a launch
+ * argument and must grow from call to call.
  */
 int kvq_peer_allgather(const void* src, size_t bytes_per_rank, void* const* dst_bufs, uint32_t* const* flag_bufs,
                        int world, int rank, uint32_t epoch, int* status, kvq_stream_t stream);

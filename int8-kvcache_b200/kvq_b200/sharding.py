@@ -73,7 +73,8 @@ class PeerGather:
     bound, the kernel uses plain peer stores) and raises RuntimeError where that is not available, in which case
     gather_outputs (NCCL) is the route. gather() must be called by every rank, the same number of times; it returns
     this step's [world * rows, ...] buffer, valid until the call after next (the two buffers alternate, because a rank
-    may run one step ahead of the slowest rank)."""
+    may run one step ahead of the slowest rank). Eager calls only: the step counter is a launch argument, so a CUDA
+    graph that captured gather() must not be replayed."""
 
     def __init__(self, rows_per_rank, row_shape, dtype, device, group=None):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # before the first symmetric allocation

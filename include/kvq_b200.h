@@ -253,20 +253,22 @@ int kvq_calib_stats(const void* key, const void* value, const int64_t* slots, in
  * vLLM's tensor parallelism, whose collectives are vLLM's. Here requests are sharded over the GPUs of one node and the
  * one exchange on the path is every rank's output rows [T / world, Hq, D] reaching all ranks; at 114 KB per rank a
  * library all-gather is pure latency (~25 us next to a ~97 us attention call), so each rank stores its rows straight
- * into every peer's gather buffer and raises a flag there (plain peer stores, bounded waits, one launch).
+ * into every peer's staging buffer and raises a flag there (plain peer stores, bounded waits, one launch).
  *   src             this rank's rows, bytes_per_rank bytes (a multiple of 16, 16-byte aligned), identical size on all ranks
- *   dst_bufs[p]     rank p's gather buffer (world * bytes_per_rank bytes) as mapped into THIS process, p < world <= 8;
- *                   row block r of every buffer receives rank r's rows. Host array, read during the call.
+ *   stage0/1[p]     rank p's two staging buffers (world * bytes_per_rank bytes each) as mapped into THIS process,
+ *                   p < world <= 8; row block r of a staging buffer receives rank r's rows; steps alternate between the
+ *                   two (a rank may be one step ahead of the slowest one). Host arrays, read during the call.
  *   flag_bufs[p]    rank p's flag array (64 uint32, zero before the first step) as mapped into this process
- *   epoch           step counter: the same value on every rank, one more every call (never reused, never reset)
+ *   out             this rank's result, world * bytes_per_rank bytes of ordinary device memory: rank r's rows at row
+ *                   block r, complete when the call's kernel has finished
+ *   counters        two uint32 in this rank's memory, zero before the first step: the kernel keeps the step count
+ *                   there, so the launch has no per-step argument and may be replayed from a CUDA graph
  *   status          device int in this rank's memory: set to 1 when a wait for a peer ran out (about a second)
- * The caller alternates between two sets of gather buffers from step to step (a rank may be one step ahead of the
- * slowest one) and orders the consumer of the gathered rows after this call on `stream`. Every rank must make the same
- * sequence of calls. One launch, no host synchronization. Not for replay from a CUDA graph: the epoch is a launch
- * argument and must grow from call to call.
+ * Every rank must make the same sequence of calls. One launch, no host synchronization, capturable.
  */
-int kvq_peer_allgather(const void* src, size_t bytes_per_rank, void* const* dst_bufs, uint32_t* const* flag_bufs,
-                       int world, int rank, uint32_t epoch, int* status, kvq_stream_t stream);
+int kvq_peer_allgather(const void* src, size_t bytes_per_rank, void* const* stage0, void* const* stage1,
+                       uint32_t* const* flag_bufs, void* out, int world, int rank, uint32_t* counters, int* status,
+                       kvq_stream_t stream);
 
 #ifdef __cplusplus
 }

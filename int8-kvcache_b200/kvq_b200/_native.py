@@ -32,7 +32,7 @@ SIGNATURES = {
     "kvq_int8_prefill_attention": (_c_int, [_c_ptr] * 9 + [ctypes.c_double, _c_int, _c_i64] + [_c_int] * 4 + [_c_i64] * 12 +
                                    [_c_int] * 3 + [_c_ptr, ctypes.c_size_t, _c_ptr]),
     "kvq_calib_stats": (_c_int, [_c_ptr] * 3 + [_c_i64, _c_int, _c_int] + [_c_i64] * 4 + [_c_ptr] * 9 + [_c_ptr]),
-    "kvq_peer_allgather": (_c_int, [_c_ptr, ctypes.c_size_t, _c_ptr, _c_ptr, _c_int, _c_int, ctypes.c_uint32, _c_ptr, _c_ptr]),
+    "kvq_peer_allgather": (_c_int, [_c_ptr, ctypes.c_size_t, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr]),
     "kvq_pages_to_wire": (_c_int, [_c_ptr] * 4 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 6 + [_c_ptr]),
     "kvq_wire_to_pages": (_c_int, [_c_ptr] * 4 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 6 + [_c_ptr]),
     "kvq_dequant_pages": (_c_int, [_c_ptr] * 9 + [_c_i64, _c_int, _c_int, _c_int] + [_c_i64] * 7 + [_c_int, _c_int, _c_ptr]),

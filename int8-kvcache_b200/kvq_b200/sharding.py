@@ -65,16 +65,16 @@ def gather_outputs(local_out, rows_per_rank, group=None, out=None):
 
 
 class PeerGather:
-    """The output all-gather as direct stores into every peer's buffer over NVLink (kvq_peer_allgather), for equal
-    shards on the GPUs of one node: ~6 us per step where a library all-gather of the same 114 KB per rank costs ~25 us.
+    """The output all-gather as direct stores into every peer's memory over NVLink (kvq_peer_allgather), for equal
+    shards on the GPUs of one node: the rows cross NVLink once, with one flag round trip, in one launch of this
+    library's own kernel instead of a library collective.
 
-    Construction is a collective over `group` (NCCL): it allocates two gather buffers and a flag array in symmetric
+    Construction is a collective over `group` (NCCL): it allocates two staging buffers and a flag array in symmetric
     memory (torch.distributed._symmetric_memory: every rank gets a mapping of every peer's copy; NVLink multicast is not
     bound, the kernel uses plain peer stores) and raises RuntimeError where that is not available, in which case
     gather_outputs (NCCL) is the route. gather() must be called by every rank, the same number of times; it returns
-    this step's [world * rows, ...] buffer, valid until the call after next (the two buffers alternate, because a rank
-    may run one step ahead of the slowest rank). Eager calls only: the step counter is a launch argument, so a CUDA
-    graph that captured gather() must not be replayed."""
+    `self.out`, the [world * rows, ...] result at a fixed address, complete in stream order. The step counter lives on
+    the device, so a CUDA graph that captured gather() can be replayed (by every rank alike)."""
 
     def __init__(self, rows_per_rank, row_shape, dtype, device, group=None):
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # before the first symmetric allocation
@@ -95,33 +95,34 @@ class PeerGather:
             raise RuntimeError(f"PeerGather: {self.bytes_per_rank} bytes per rank is not a multiple of 16")
         self.lib, self._check = _native.lib(), _native.check
         device = torch.device(device)
-        self.full = [symm_mem.empty((self.world * self.rows,) + self.row_shape, dtype=dtype, device=device) for _ in range(2)]
+        full_shape = (self.world * self.rows,) + self.row_shape
+        self.stage = [symm_mem.empty(full_shape, dtype=dtype, device=device) for _ in range(2)]
         self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)
         self.flags.zero_()
-        handles = [symm_mem.rendezvous(t, self.group) for t in self.full]
+        handles = [symm_mem.rendezvous(t, self.group) for t in self.stage]
         flag_handle = symm_mem.rendezvous(self.flags, self.group)
         self._handles = handles + [flag_handle]   # the mappings live as long as this object
         ptrs = ctypes.c_void_p * self.world
-        self._dst = [ptrs(*[int(p) for p in h.buffer_ptrs]) for h in handles]
+        self._stage_ptrs = [ptrs(*[int(p) for p in h.buffer_ptrs]) for h in handles]
         self._flag_ptrs = ptrs(*[int(p) for p in flag_handle.buffer_ptrs])
+        self.out = torch.empty(full_shape, dtype=dtype, device=device)
+        self.counters = torch.zeros(2, dtype=torch.int32, device=device)   # completed steps, finished blocks
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
-        self.epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)   # every rank's flags are zero before anyone signals
 
     def gather(self, local_out):
-        """Store this rank's rows [rows, ...] into every rank's buffer of this step and wait (on the device, bounded)
-        for everyone else's; returns the gathered [world * rows, ...] tensor. Asynchronous on the current stream."""
+        """Store this rank's rows [rows, ...] into every rank's staging buffer of this step, wait (on the device,
+        bounded) for everyone else's and collect them in `self.out`, which is returned. Asynchronous on the current
+        stream; capturable."""
         if tuple(local_out.shape) != (self.rows,) + self.row_shape or local_out.dtype != self.dtype or \
                 not local_out.is_contiguous():
             raise ValueError(f"PeerGather.gather: expected a contiguous {(self.rows,) + self.row_shape} {self.dtype} tensor")
-        self.epoch += 1
-        which = self.epoch & 1
-        self._check(self.lib.kvq_peer_allgather(local_out.data_ptr(), self.bytes_per_rank, self._dst[which],
-                                                self._flag_ptrs, self.world, self.rank, self.epoch & 0xffffffff,
-                                                self.status.data_ptr(),
+        self._check(self.lib.kvq_peer_allgather(local_out.data_ptr(), self.bytes_per_rank, self._stage_ptrs[0],
+                                                self._stage_ptrs[1], self._flag_ptrs, self.out.data_ptr(), self.world,
+                                                self.rank, self.counters.data_ptr(), self.status.data_ptr(),
                                                 torch.cuda.current_stream(local_out.device).cuda_stream))
-        return self.full[which]
+        return self.out
 
     def check(self):
         """Synchronizes and raises if a wait for a peer ran out since the last check (a rank that never arrived)."""

@@ -111,6 +111,24 @@ def _peer_gather_worker(rank, world, port, result_path):
         # the NCCL route gives the same rows
         ok = ok and torch.equal(sharding.gather_outputs(local, [rows] * world).cpu(), full)
     pg.check()
+    # replay from a CUDA graph: the step counter lives on the device
+    src = torch.zeros(rows, *shape, dtype=torch.bfloat16, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        pg.gather(src)                       # warm-up on the capture stream (both ranks alike)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        res = pg.gather(src)
+    for step in range(3):
+        gen = torch.Generator().manual_seed(200 + step)
+        full = torch.randn(world * rows, *shape, generator=gen).to(torch.bfloat16)
+        src.copy_(full[rank * rows:(rank + 1) * rows])
+        graph.replay()
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(res.cpu(), full)
+    pg.check()
     try:
         pg.gather(local[:1])
         ok = False

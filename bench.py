@@ -347,63 +347,75 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- strong scaling: the FIXED headline layer (128 requests in total) sharded 128 / N requests per GPU, with the
     #      NCCL all-gather of every rank's output rows inside the timed step ----
-    strong = None
-    if (batch, ctx, q_len) == (BATCH, CTX, 1) and BATCH % world == 0:
-        from kvq_b200 import sharding
+    strong, strong_error = None, None
+    collective, strong_graphed = "none (one GPU)", False
+    try:
+        if (batch, ctx, q_len) == (BATCH, CTX, 1) and BATCH % world == 0:
+            from kvq_b200 import sharding
 
-        n = BATCH // world
-        q_n, out_n, cu_n, sl_n, bt_n = q[:n], out[:n], cu[:n + 1], sl[:n], bt[:n]
-        gathered = torch.empty(BATCH, HQ, D, dtype=out.dtype, device=dev) if world > 1 else None
-        # the gather: this library's peer-store kernel over NVLink where symmetric memory is available, else NCCL
-        peer, collective = None, "none (one GPU)"
-        if world > 1:
-            collective = f"NCCL all_gather of [{n}, {HQ}, {D}] bf16 output rows per rank inside the timed step"
-            try:
-                if os.environ.get("KVQ_GATHER", "peer") == "peer":
-                    peer = sharding.PeerGather(n, (HQ, D), out.dtype, dev)
-                    collective = (f"kvq_peer_allgather: every rank stores its [{n}, {HQ}, {D}] bf16 output rows into every "
-                                  "peer's buffer over NVLink and waits for the peers' flags, inside the timed step")
-            except Exception as e:   # no symmetric memory on this box: the library route
-                collective += f" (peer route unavailable: {type(e).__name__})"
-        out_c = out_n.contiguous()
+            n = BATCH // world
+            q_n, out_n, cu_n, sl_n, bt_n = q[:n], out[:n], cu[:n + 1], sl[:n], bt[:n]
+            gathered = torch.empty(BATCH, HQ, D, dtype=out.dtype, device=dev) if world > 1 else None
+            # the gather: this library's peer-store kernel over NVLink where symmetric memory is available, else NCCL
+            peer, collective = None, "none (one GPU)"
+            if world > 1:
+                collective = f"NCCL all_gather of [{n}, {HQ}, {D}] bf16 output rows per rank inside the timed step"
+                try:
+                    if os.environ.get("KVQ_GATHER", "peer") == "peer":
+                        peer = sharding.PeerGather(n, (HQ, D), out.dtype, dev)
+                        collective = (f"kvq_peer_allgather: every rank stores its [{n}, {HQ}, {D}] bf16 output rows into every "
+                                      "peer's buffer over NVLink and waits for the peers' flags, inside the timed step")
+                except Exception as e:   # no symmetric memory on this box: the library route
+                    peer = None
+                    collective += f" (peer route unavailable: {type(e).__name__})"
+                agreed = torch.tensor([1 if peer is not None else 0], device=dev)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN)   # every rank takes the same route
+                if int(agreed.item()) == 0 and peer is not None:
+                    peer = None
+                    collective = (f"NCCL all_gather of [{n}, {HQ}, {D}] bf16 output rows per rank inside the timed step "
+                                  "(peer route unavailable on another rank)")
+            out_c = out_n.contiguous()
 
-        def strong_step():
-            ck.decode_attention(q_n, kq, vq, out_c, cu_n, sl_n, bt_n, scale, st, max_query_len=1)
+            def strong_step():
+                ck.decode_attention(q_n, kq, vq, out_c, cu_n, sl_n, bt_n, scale, st, max_query_len=1)
+                if peer is not None:
+                    peer.gather(out_c)
+                elif world > 1:
+                    sharding.gather_outputs(out_c, [n] * world, out=gathered)
+
+            for _ in range(3):
+                strong_step()
+            sync_all()
+            # one step = one CUDA graph replay (attention call + gather), as a serving engine would run a decode step
+            run_step, strong_graphed = strong_step, False
+            if os.environ.get("KVQ_STRONG_GRAPH", "1") == "1":
+                try:
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        strong_step()
+                    torch.cuda.current_stream().wait_stream(side)
+                    sgraph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(sgraph):
+                        strong_step()
+                    run_step, strong_graphed = sgraph.replay, True
+                except Exception:   # capture not possible here (e.g. the collective): eager steps
+                    torch.cuda.synchronize()
+            for _ in range(2):
+                run_step()
+            sync_all()
+            s_start, s_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s_start.record()
+            for _ in range(args.steps):
+                run_step()
+            s_stop.record()
+            sync_all()
+            strong = s_start.elapsed_time(s_stop)
             if peer is not None:
-                peer.gather(out_c)
-            elif world > 1:
-                sharding.gather_outputs(out_c, [n] * world, out=gathered)
-
-        for _ in range(3):
-            strong_step()
-        sync_all()
-        # one step = one CUDA graph replay (attention call + gather), as a serving engine would run a decode step
-        run_step, strong_graphed = strong_step, False
-        if os.environ.get("KVQ_STRONG_GRAPH", "1") == "1":
-            try:
-                side = torch.cuda.Stream()
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side):
-                    strong_step()
-                torch.cuda.current_stream().wait_stream(side)
-                sgraph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(sgraph):
-                    strong_step()
-                run_step, strong_graphed = sgraph.replay, True
-            except Exception:   # capture not possible here (e.g. the collective): eager steps
-                torch.cuda.synchronize()
-        for _ in range(2):
-            run_step()
-        sync_all()
-        s_start, s_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s_start.record()
-        for _ in range(args.steps):
-            run_step()
-        s_stop.record()
-        sync_all()
-        strong = s_start.elapsed_time(s_stop)
-        if peer is not None:
-            peer.check()   # raises if a wait for a peer's rows ran out
+                peer.check()   # raises if a wait for a peer's rows ran out
+    except Exception as e:   # the headline line is still printed; the record says what happened
+        strong, strong_error = None, f"{type(e).__name__}: {e}"[:300]
+        torch.cuda.synchronize()
 
     # ---- output check: a seeded subset of the timed batch recomputed by the CPU oracle ----
     check = output_check(case, out_ref=None, ck=ck, rank=rank) if rank == 0 and not args.no_check else None
@@ -445,6 +457,8 @@ def run_ours(args, rank, world, local_rank):
     }
     if check is not None:
         line["output_check"] = check
+    if strong_error is not None:
+        line["strong"] = {"error": strong_error}
     if strong is not None:
         s_ms = strong / args.steps
         line["strong"] = {

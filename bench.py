@@ -470,7 +470,10 @@ def run_ours(args, rank, world, local_rank):
             "note": "the weak-scaling step above runs the whole 128-request layer on every GPU, so its time is this "
                     "run's one-GPU time for the fixed layer"}
     if world == 1 and not args.no_cpu:
-        line["cpu_baseline"] = cpu_baseline()
+        try:
+            line["cpu_baseline"] = cpu_baseline()
+        except Exception as e:   # never lose the GPU line to the CPU leg
+            line["cpu_baseline"] = {"error": f"{type(e).__name__}: {e}"[:300]}
     return line
 
 
@@ -844,7 +847,10 @@ def main():
         headline = (args.batch, args.ctx, args.q_len) == (BATCH, CTX, 1) and not args.profile
         if headline and not args.no_model_step and args.model_requests % world == 0:
             torch.cuda.empty_cache()
-            ms = model_step_record(args, rank, world, dev, min(args.steps, 10))
+            try:
+                ms = model_step_record(args, rank, world, dev, min(args.steps, 10))
+            except Exception as e:   # the headline line is still printed; the record says what happened
+                ms = {"workload": "model_step", "error": f"{type(e).__name__}: {e}"[:300]}
             if line is not None:
                 line["model_step"] = ms
     if rank == 0 and line is not None:

@@ -418,7 +418,12 @@ def run_ours(args, rank, world, local_rank):
         torch.cuda.synchronize()
 
     # ---- output check: a seeded subset of the timed batch recomputed by the CPU oracle ----
-    check = output_check(case, out_ref=None, ck=ck, rank=rank) if rank == 0 and not args.no_check else None
+    check = None
+    if rank == 0 and not args.no_check:
+        try:
+            check = output_check(case, out_ref=None, ck=ck, rank=rank)
+        except Exception as e:   # the checker failing to run is reported, not fatal to the measurement
+            check = {"ok": False, "error": f"{type(e).__name__}: {e}"[:300]}
 
     if world > 1:
         t = torch.tensor([elapsed_ms, e2e_ms, strong or 0.0], device=dev)

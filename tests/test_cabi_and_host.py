@@ -467,3 +467,23 @@ def test_decode_split_is_contiguous_cost_balanced_and_snaps_to_items():
         starts = {first for first, _ in items}
         snapped[cost] = sum(1 for u in rb if u in starts)
     assert snapped[20] >= 4 * snapped[0]
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` (the reference's CPU implementation on the host cores) runs without a GPU and prints
+    one JSON line with the keys the measurement contract names."""
+    import json
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=root)
+    assert res.returncode == 0, res.stderr[-500:]
+    line = json.loads([ln for ln in res.stdout.splitlines() if ln.startswith("{")][-1])
+    assert line["impl"] == "reference" and line["unit"] == "GB/s" and line["higher_is_better"] is True
+    assert line["metric"] == "int8_paged_decode_attention_kv_bandwidth_128x32k" and line["steps"] == 1
+    assert line["value"] > 0 and line["e2e"]["value"] == line["value"]
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+    assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] >= 1
+    assert "workload" in line["config"] and line["gpu_launches"] == 0

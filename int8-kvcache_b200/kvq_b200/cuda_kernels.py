@@ -124,13 +124,16 @@ class _StreamWorkspaces:
         self.live, self.retired = {}, []
 
     @staticmethod
-    def _key(device):
-        device = torch.device(device)   # "cuda", "cuda:1" and torch.device objects name the same buffers
+    def _key(device, stream_ptr=None):
+        if not isinstance(device, torch.device):
+            device = torch.device(device)   # "cuda", "cuda:1" and torch.device objects name the same buffers
         index = device.index if device.index is not None else torch.cuda.current_device()
-        return index, torch.cuda.current_stream(device).cuda_stream
+        return index, (torch.cuda.current_stream(device).cuda_stream if stream_ptr is None else stream_ptr)
 
-    def get(self, device, need):
-        key = self._key(device)
+    def get(self, device, need, stream_ptr=None):
+        """The buffer of (device, stream); stream_ptr: the raw handle of torch's current stream on `device` when the
+        caller has looked it up already."""
+        key = self._key(device, stream_ptr)
         ws = self.live.get(key)
         if ws is None or ws.numel() < need:
             if ws is not None:
@@ -147,12 +150,18 @@ class _StreamWorkspaces:
 _WORKSPACES = _StreamWorkspaces(lambda n, d: ext().kvq_decode_workspace_size(n, d), (4096, 128))
 
 
-def decode_workspace(device, num_seqs, head_dim):
+_WORKSPACE_BYTES = {}   # (num_seqs, head_dim) -> kvq_decode_workspace_size: asked once per batch size
+
+
+def decode_workspace(device, num_seqs, head_dim, stream_ptr=None):
     """Scratch of the attention kernels (work plan and split-KV partials) for torch's current stream on `device`."""
-    need = ext().kvq_decode_workspace_size(num_seqs, head_dim)
-    if need == 0:
-        raise RuntimeError("kvq_b200: " + ext().kvq_last_error().decode())
-    return _WORKSPACES.get(device, need)
+    need = _WORKSPACE_BYTES.get((num_seqs, head_dim))
+    if need is None:
+        need = ext().kvq_decode_workspace_size(num_seqs, head_dim)
+        if need == 0:
+            raise RuntimeError("kvq_b200: " + ext().kvq_last_error().decode())
+        _WORKSPACE_BYTES[(num_seqs, head_dim)] = need
+    return _WORKSPACES.get(device, need, stream_ptr)
 
 
 # Channels per q scale inside the attention kernel: unset / 0 = one scale per (token, head) row, the reference CUDA
@@ -187,13 +196,14 @@ def decode_attention(q, k_cache, v_cache, out, cu_seqlens_q, seq_lens, block_tab
     kc, kc_sb, kc_sn, kc_sh = _cache_args(k_cache)
     vc, vc_sb, vc_sn, vc_sh = _cache_args(v_cache)
     pk, pv = _scale_flags(ks, vs)
-    ws = decode_workspace(q.device, num_seqs, q.size(2))
+    stream = torch.cuda.current_stream(q.device).cuda_stream   # looked up once: launch stream and workspace key
+    ws = decode_workspace(q.device, num_seqs, q.size(2), stream)
     _native.check(ext().kvq_int8_decode_attention_qgroup(
         q.data_ptr(), kc, vc, out.data_ptr(), cu_seqlens_q.data_ptr(), seq_lens.data_ptr(), block_table.data_ptr(),
         ks.data_ptr(), vs.data_ptr(), float(softmax_scale), num_seqs, q.size(1), k_cache.size(2), q.size(2),
         k_cache.size(1), k_cache.size(0), q.stride(0), q.stride(1), out.stride(0), out.stride(1), kc_sb, kc_sn, kc_sh,
         vc_sb, vc_sn, vc_sh, block_table.stride(0), pk, pv, int(max_query_len), SHORT_Q,
-        int(Q_GROUP if q_group is None else q_group), ws.data_ptr(), ws.numel(), _stream()))
+        int(Q_GROUP if q_group is None else q_group), ws.data_ptr(), ws.numel(), stream))
     return out
 
 
